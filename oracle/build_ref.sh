@@ -1,0 +1,104 @@
+#!/usr/bin/env bash
+# Builds oracle/_ref/ref_harness: the UNMODIFIED-in-behaviour GradCraft CPU path (CPUBackend +
+# OpenBLAS cblas_sgemm + the naive nodes) driven by oracle/ref_harness.cpp.
+#
+# The reference ships for MSVC only, so a scratch copy of its headers (never committed, never
+# placed in this repository) receives four mechanical portability patches before g++ sees it:
+#   1. constructor template-ids (`AddNode<T>(...)`)            -> plain constructor names
+#   2. constrained friend templates that GCC treats as new overloads -> members made public
+#   3. `std::sqrtf`                                             -> `sqrtf`
+#   4. `<corecrt_malloc.h>` / `<cblas.h>`                       -> two shim headers
+# None of the patches touches arithmetic.  Outputs go to oracle/_ref/ only.
+#
+# Usage: oracle/build_ref.sh [reference_root]     (default /root/reference)
+set -euo pipefail
+HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+REF="${1:-/root/reference}"
+OUT="$HERE/_ref"
+if [ ! -d "$REF/gradc" ]; then
+  echo "build_ref: reference tree not found at $REF (prebuilt oracle/_ref is used as is)"; exit 0
+fi
+SCRATCH="$(mktemp -d /tmp/gradc_ref_build.XXXXXX)"
+trap 'rm -rf "$SCRATCH"' EXIT
+mkdir -p "$OUT" "$SCRATCH/shim" "$SCRATCH/ref"
+cp -r "$REF/gradc" "$SCRATCH/ref/gradc"
+chmod -R u+w "$SCRATCH/ref"
+
+# --- shim headers -----------------------------------------------------------------------------
+cat > "$SCRATCH/shim/corecrt_malloc.h" <<'H'
+#pragma once
+#include <cstdlib>
+static inline void* _aligned_malloc(size_t bytes, size_t align) {
+    void* p = nullptr; if (bytes == 0) bytes = align;
+    return posix_memalign(&p, align, bytes) == 0 ? p : nullptr; }
+static inline void _aligned_free(void* p) { free(p); }
+H
+cat > "$SCRATCH/shim/cblas.h" <<'H'
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+typedef int blasint;
+typedef enum CBLAS_ORDER { CblasRowMajor = 101, CblasColMajor = 102 } CBLAS_ORDER;
+typedef enum CBLAS_TRANSPOSE { CblasNoTrans = 111, CblasTrans = 112, CblasConjTrans = 113 } CBLAS_TRANSPOSE;
+void cblas_sgemm(CBLAS_ORDER, CBLAS_TRANSPOSE, CBLAS_TRANSPOSE, blasint M, blasint N, blasint K, float alpha,
+                 const float* A, blasint lda, const float* B, blasint ldb, float beta, float* C, blasint ldc);
+void cblas_dgemm(CBLAS_ORDER, CBLAS_TRANSPOSE, CBLAS_TRANSPOSE, blasint M, blasint N, blasint K, double alpha,
+                 const double* A, blasint lda, const double* B, blasint ldb, double beta, double* C, blasint ldc);
+void openblas_set_num_threads(int);
+int openblas_get_num_threads(void);
+#ifdef __cplusplus
+}
+#endif
+H
+
+# --- portability patches ----------------------------------------------------------------------
+G="$SCRATCH/ref/gradc"
+sed -i -E 's/^(\s*)(AddNode|SubNode|MulNode|DivNode|NormalMatMulNode|BatchedMatMulNode)<T>\(/\1\2(/' "$G/graph/nodes/math_nodes.hpp"
+# friend operator/matmul/blas-meta templates: drop the declarations, open the members instead
+python3 - "$G/core/tensor.hpp" <<'PY'
+import re, sys
+p = sys.argv[1]
+lines = open(p).read().split("\n")
+out = []
+for l in lines:
+    st = l.strip()
+    is_friend_fn = "friend" in st and "(" in st and "friend class" not in st
+    if is_friend_fn:
+        # drop the declaration and the template/requires header lines that belong to it
+        if not st.startswith("template"):
+            while out and (out[-1].strip().startswith("template <") or out[-1].strip().startswith("requires")):
+                out.pop()
+        continue
+    out.append(l)
+s = "\n".join(out)
+s = s.replace("        private:\n            std::vector<int64_t> m_shape;", "        public:\n            std::vector<int64_t> m_shape;", 1)
+open(p, "w").write(s)
+PY
+sed -i 's/std::sqrtf/sqrtf/g' "$G/backend/cuda/math_functors.cuh"
+
+OPENBLAS="$(python3 - <<'PY'
+import glob, sysconfig, os
+sp = sysconfig.get_paths()["purelib"]
+c = sorted(glob.glob(os.path.join(sp, "opencv_python_headless.libs", "libopenblas*.so*")))
+print(c[0] if c else "")
+PY
+)"
+CXXFLAGS="-std=c++23 -O2 -fopenmp -w -I$SCRATCH/shim -I$SCRATCH/ref -I/usr/local/cuda/include"
+if [ -n "$OPENBLAS" ]; then
+  BLASDIR="$(dirname "$OPENBLAS")"
+  echo "build_ref: OpenBLAS = $OPENBLAS"
+  g++ $CXXFLAGS "$HERE/ref_harness.cpp" -o "$OUT/ref_harness" \
+      "$OPENBLAS" -Wl,--disable-new-dtags -Wl,-rpath,"$BLASDIR" -Wl,--allow-shlib-undefined \
+      -L/usr/local/cuda/lib64 -lcudart -Wl,-rpath,/usr/local/cuda/lib64 \
+      -Wl,--unresolved-symbols=ignore-all -fopenmp
+  echo "openblas" > "$OUT/blas_kind.txt"
+else
+  echo "build_ref: no OpenBLAS found; linking the plain triple-loop sgemm in oracle/naive_cblas.c"
+  gcc -O3 -march=native -fopenmp -c "$HERE/naive_cblas.c" -o "$SCRATCH/naive_cblas.o"
+  g++ $CXXFLAGS "$HERE/ref_harness.cpp" "$SCRATCH/naive_cblas.o" -o "$OUT/ref_harness" \
+      -L/usr/local/cuda/lib64 -lcudart -Wl,-rpath,/usr/local/cuda/lib64 \
+      -Wl,--unresolved-symbols=ignore-all -fopenmp
+  echo "naive" > "$OUT/blas_kind.txt"
+fi
+echo "build_ref: wrote $OUT/ref_harness"

@@ -1,0 +1,98 @@
+"""Regenerates the golden fixtures in this directory from the compiled reference CPU path.
+
+Run in a container that has the reference tree:  oracle/build_ref.sh && python tests/golden/make_golden.py
+Inputs are seeded (oracle/synth.py, numpy default_rng); outputs are whatever oracle/_ref/ref_harness
+(GradCraft's CPUBackend + OpenBLAS) computes for them.  The .npz files are what the tests read; the
+harness itself is never needed at test time.
+"""
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+from oracle import ckpt, synth  # noqa: E402
+
+HARNESS = os.path.join(ROOT, "oracle", "_ref", "ref_harness")
+
+
+def op_inputs(seed=0):
+    r = np.random.default_rng(seed)
+    n = lambda *s: r.standard_normal(s, dtype=np.float32)
+    d = {}
+    # odd widths on purpose: not multiples of 4 / 32
+    d["ln.x"], d["ln.gamma"], d["ln.beta"], d["ln.dy"] = n(3, 7, 50) * 2 + 0.5, n(50) * 0.2 + 1, n(50) * 0.1, n(3, 7, 50) * 0.01
+    d["ln.eps"] = np.array([1e-5], np.float32)
+    d["rms.x"], d["rms.gamma"], d["rms.dy"] = n(3, 7, 50), n(50) * 0.2 + 1, n(3, 7, 50) * 0.01
+    d["rms.eps"] = np.array([1e-5], np.float32)
+    d["gelu.x"], d["gelu.dy"] = n(5, 37) * 2, n(5, 37) * 0.01
+    d["swiglu.a"], d["swiglu.b"], d["swiglu.dy"] = n(5, 37) * 2, n(5, 37), n(5, 37) * 0.01
+    d["csm.scores"], d["csm.dy"] = n(2, 3, 19, 19) * 3, n(2, 3, 19, 19) * 0.01
+    d["csm.scale"] = np.array([0.35355338], np.float32)
+    d["ce.logits"] = n(13, 101) * 3
+    d["ce.targets"] = r.integers(0, 101, 13).astype(np.float32)
+    d["ce.eps"] = np.array([1e-5], np.float32)
+    d["ce.upstream"] = np.array([0.25], np.float32)
+    d["emb.table"] = n(23, 12)
+    d["emb.idx"] = synth.zipf_tokens(5, 3 * 17, 23).reshape(3, 17).astype(np.float32)
+    d["emb.dy"] = n(3, 17, 12) * 0.01
+    d["lin.x"], d["lin.W"], d["lin.b"], d["lin.dy"] = n(3, 5, 24), n(24, 20) * 0.1, n(20) * 0.1, n(3, 5, 20) * 0.01
+    d["attn.q"], d["attn.k"], d["attn.v"], d["attn.dy"] = n(2, 3, 19, 8), n(2, 3, 19, 8), n(2, 3, 19, 8), n(2, 3, 19, 8) * 0.01
+    d["adamw.w"] = n(9, 7) * 0.02
+    d["adamw.hyper"] = np.array([3e-4, 0.9, 0.95, 0.1, 1e-5, 3, 1.0, 0], np.float32)
+    for s in range(3):
+        d["adamw.g%d" % s] = n(9, 7) * (0.5 if s else 3.0)  # step 0 clips, later steps may not
+    return d
+
+
+def run_ops(tmp):
+    d = op_inputs()
+    ckpt.save(os.path.join(tmp, "in.ckpt"), d)
+    subprocess.run([HARNESS, "ops", os.path.join(tmp, "in.ckpt"), os.path.join(tmp, "out.ckpt")], check=True)
+    out = ckpt.load(os.path.join(tmp, "out.ckpt"))
+    np.savez_compressed(os.path.join(HERE, "ops.npz"), **{"in." + k: v for k, v in d.items()}, **{"out." + k: v for k, v in out.items()})
+    print("ops:", len(out), "outputs")
+
+
+GPT_CASES = {
+    # name: arch, V, T, C, H, L, F, B, steps, accum, clip, perturb
+    "config1_lngelu": ("lngelu", 512, 64, 128, 4, 2, 512, 4, 10, 1, 0.0, False),  # BASELINE config 1
+    "mini_lngelu": ("lngelu", 96, 16, 32, 4, 2, 80, 3, 3, 2, 1.0, True),
+    "mini_rmsswiglu": ("rmsswiglu", 96, 16, 32, 4, 2, 96, 3, 3, 2, 1.0, True),
+}
+HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, wd=0.1, eps=1e-5, norm_eps=1e-5)
+
+
+def run_gpt(tmp, name):
+    arch, V, T, C, H, L, F, B, steps, accum, clip, perturb = GPT_CASES[name]
+    w = synth.gpt_weights(arch, V, T, C, H, L, F, seed=0, perturb=perturb)
+    batches = synth.token_batches(1234, steps * accum, B, T, V)
+    ckpt.save(os.path.join(tmp, "w.ckpt"), w)
+    batches.tofile(os.path.join(tmp, "tok.i64"))
+    prefix = os.path.join(tmp, name)
+    h = HYPER
+    cmd = [HARNESS, "gpt", arch] + [str(v) for v in (V, T, C, H, L, F, B, steps, accum, h["lr"], h["beta1"], h["beta2"], h["wd"], h["eps"], clip)]
+    cmd += [os.path.join(tmp, "w.ckpt"), os.path.join(tmp, "tok.i64"), prefix, str(h["norm_eps"])]
+    subprocess.run(cmd, check=True)
+    rows = np.loadtxt(prefix + "_loss.txt", dtype=np.float64).reshape(steps, 2)
+    out = {"loss": rows[:, 0].astype(np.float32), "norm": rows[:, 1].astype(np.float32)}
+    for k in (1, steps):
+        for n_, a in ckpt.load("%s_grads%d.ckpt" % (prefix, k)).items():
+            out["grads%d/%s" % (k, n_)] = a
+    for n_, a in ckpt.load("%s_weights%d.ckpt" % (prefix, steps)).items():
+        out["weights%d/%s" % (steps, n_)] = a
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+    print(name, "loss", out["loss"])
+
+
+if __name__ == "__main__":
+    if not os.path.exists(HARNESS):
+        sys.exit("oracle/_ref/ref_harness missing: run oracle/build_ref.sh first")
+    with tempfile.TemporaryDirectory() as tmp:
+        run_ops(tmp)
+        for name in GPT_CASES:
+            run_gpt(tmp, name)

@@ -1,0 +1,130 @@
+"""The numpy oracle against fixtures produced by the compiled reference CPU path (CPU-only tests)."""
+import numpy as np
+import pytest
+
+from oracle import numpy_oracle as O
+from oracle import synth
+from tests.helpers import assert_grads_close, load_golden, max_abs_rel, split_prefix
+
+TOL = 2e-6  # fp32 restatement vs fp32 reference: differences are summation order only
+
+
+@pytest.fixture(scope="module")
+def ops():
+    g = load_golden("ops")
+    return split_prefix(g, "in."), split_prefix(g, "out.")
+
+
+def test_layernorm(ops):
+    i, o = ops
+    y, mu, rstd = O.layernorm_fwd(i["ln.x"], i["ln.gamma"], i["ln.beta"], float(i["ln.eps"][0]))
+    dx, dg, db = O.layernorm_bwd(i["ln.dy"], i["ln.x"], i["ln.gamma"], mu, rstd)
+    for a, k in ((y, "ln.y"), (dx, "ln.dx"), (dg, "ln.dgamma"), (db, "ln.dbeta")):
+        assert max_abs_rel(a, o[k]) < TOL, k
+
+
+def test_rmsnorm(ops):
+    i, o = ops
+    y, inv = O.rmsnorm_fwd(i["rms.x"], i["rms.gamma"], float(i["rms.eps"][0]))
+    dx, dg = O.rmsnorm_bwd(i["rms.dy"], i["rms.x"], i["rms.gamma"], inv)
+    for a, k in ((y, "rms.y"), (dx, "rms.dx"), (dg, "rms.dgamma")):
+        assert max_abs_rel(a, o[k]) < TOL, k
+
+
+def test_gelu_swiglu(ops):
+    i, o = ops
+    assert max_abs_rel(O.gelu_fwd(i["gelu.x"]), o["gelu.y"]) < TOL
+    assert max_abs_rel(O.gelu_bwd(i["gelu.dy"], i["gelu.x"]), o["gelu.dx"]) < TOL
+    assert max_abs_rel(O.swiglu_fwd(i["swiglu.a"], i["swiglu.b"]), o["swiglu.y"]) < TOL
+    da, db = O.swiglu_bwd(i["swiglu.dy"], i["swiglu.a"], i["swiglu.b"])
+    assert max_abs_rel(da, o["swiglu.da"]) < TOL
+    assert max_abs_rel(db, o["swiglu.db"]) < TOL
+
+
+def test_causal_softmax(ops):
+    i, o = ops
+    p = O.causal_softmax_fwd(i["csm.scores"], float(i["csm.scale"][0]))
+    assert max_abs_rel(p, o["csm.probs"]) < TOL
+    assert np.all(np.triu(p, 1) == 0)
+    assert max_abs_rel(O.causal_softmax_bwd(i["csm.dy"], p, float(i["csm.scale"][0])), o["csm.dscores"]) < TOL
+
+
+def test_softmax_ce(ops):
+    i, o = ops
+    t = i["ce.targets"].astype(np.int64)
+    loss, p = O.softmax_ce_fwd(i["ce.logits"], t, float(i["ce.eps"][0]))
+    assert abs(float(loss) - float(o["ce.loss"])) / abs(float(o["ce.loss"])) < 1e-6
+    assert max_abs_rel(O.softmax_ce_bwd(p, t, float(i["ce.upstream"][0])), o["ce.dlogits"]) < TOL
+
+
+def test_embedding(ops):
+    i, o = ops
+    idx = i["emb.idx"].astype(np.int64)
+    assert np.array_equal(O.embed_fwd(idx, i["emb.table"]), o["emb.y"])
+    d = O.scatter_add(np.zeros_like(i["emb.table"]), idx, i["emb.dy"])
+    assert max_abs_rel(d, o["emb.dtable"]) < TOL
+    # integer bookkeeping: the rows that received gradient are exactly the rows hit by an index
+    order, counts, offsets = O.scatter_plan(idx, i["emb.table"].shape[0])
+    assert np.array_equal(counts > 0, np.abs(o["emb.dtable"]).sum(axis=1) > 0)
+    assert counts.sum() == idx.size and offsets[-1] == idx.size
+    assert np.array_equal(np.sort(order), np.arange(idx.size))
+    assert np.all(np.diff(idx.reshape(-1)[order]) >= 0)
+
+
+def test_linear_attention(ops):
+    i, o = ops
+    assert max_abs_rel(O.linear_fwd(i["lin.x"], i["lin.W"], i["lin.b"]), o["lin.y"]) < TOL
+    dx, dW, db = O.linear_bwd(i["lin.dy"], i["lin.x"], i["lin.W"])
+    for a, k in ((dx, "lin.dx"), (dW, "lin.dW"), (db, "lin.db")):
+        assert max_abs_rel(a, o[k]) < TOL, k
+    out, p = O.attention_fwd(i["attn.q"], i["attn.k"], i["attn.v"])
+    assert max_abs_rel(out, o["attn.o"]) < TOL
+    dq, dk, dv = O.attention_bwd(i["attn.dy"], i["attn.q"], i["attn.k"], i["attn.v"], p)
+    for a, k in ((dq, "attn.dq"), (dk, "attn.dk"), (dv, "attn.dv")):
+        assert max_abs_rel(a, o[k]) < TOL, k
+
+
+def test_adamw_with_clip(ops):
+    i, o = ops
+    lr, b1, b2, wd, eps, steps, clip, nd = [float(x) for x in i["adamw.hyper"]]
+    w = i["adamw.w"].copy()
+    m, v = np.zeros_like(w), np.zeros_like(w)
+    b1e = b2e = np.float32(1.0)
+    for s in range(int(steps)):
+        g = {"w": i["adamw.g%d" % s].copy()}
+        n = O.global_norm_clip(g, clip)
+        assert abs(float(n) - float(o["adamw.norm%d" % s])) / float(n) < 1e-6
+        b1e, b2e = np.float32(b1e * np.float32(b1)), np.float32(b2e * np.float32(b2))
+        w, m, v = O.adamw_step(w, g["w"], m, v, lr, b1, b2, b1e, b2e, wd, eps, bool(nd))
+    assert max_abs_rel(w, o["adamw.w_out"]) < TOL
+    assert max_abs_rel(m, o["adamw.m_out"]) < TOL
+    assert max_abs_rel(v, o["adamw.v_out"]) < TOL
+
+
+@pytest.mark.parametrize("name", ["config1_lngelu", "mini_lngelu", "mini_rmsswiglu"])
+def test_gpt_training_matches_reference(name):
+    from tests.golden.make_golden import GPT_CASES, HYPER
+
+    arch, V, T, C, H, L, F, B, steps, accum, clip, perturb = GPT_CASES[name]
+    gold = load_golden(name)
+    w = synth.gpt_weights(arch, V, T, C, H, L, F, seed=0, perturb=perturb)
+    batches = synth.token_batches(1234, steps * accum, B, T, V)
+    model = O.GPTOracle(arch, V, T, C, H, L, F, HYPER["norm_eps"], 1e-5)
+    losses, grads, weights = model.train(w, batches, steps, accum, HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["wd"], HYPER["eps"], clip, record=(1, steps))
+    rel = np.abs(np.array(losses) - gold["loss"]) / np.abs(gold["loss"])
+    assert rel.max() < 1e-5, rel
+    for k in (1, steps):
+        assert_grads_close(grads[k], split_prefix(gold, "grads%d/" % k), tol=1e-4)
+    ref_w = split_prefix(gold, "weights%d/" % steps)
+    for k_, a in weights[steps].items():
+        assert float(np.abs(a - ref_w[k_]).max()) < 2e-5, k_
+
+
+def test_synth_streams_are_stable():
+    t = synth.zipf_tokens(7, 1000, 512)
+    assert t.min() >= 0 and t.max() < 512
+    assert np.array_equal(t[10:20], synth.zipf_tokens(7, 10, 512, start=10))
+    # Zipf(1.1): token 0 is the most frequent
+    assert np.bincount(t, minlength=512).argmax() == 0
+    w = synth.normal(0, "x.W", (64, 64), 0.02)
+    assert abs(float(w.std()) - 0.02) < 2e-3 and abs(float(w.mean())) < 2e-3
