@@ -1,0 +1,125 @@
+// Internal helpers shared by the sm_100a kernels: context layout, error plumbing, vector access and
+// warp/block reductions.  Not part of the public ABI (include/gradc_b200.h is).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/gradc_b200.h"
+
+namespace gcb {
+
+constexpr int kSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized as multiples of this
+
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define GCB_CHECK_CUDA(expr)                                              \
+    do {                                                                  \
+        cudaError_t _e = (expr);                                          \
+        if (_e != cudaSuccess) return gcb::cuda_fail(_e, #expr);          \
+    } while (0)
+
+#define GCB_REQUIRE(cond, ...)                                            \
+    do {                                                                  \
+        if (!(cond)) {                                                    \
+            gcb::set_error(__VA_ARGS__);                                  \
+            return GCB_INVALID_ARG;                                       \
+        }                                                                 \
+    } while (0)
+
+// Stream-ordered arena.  Device memory is reserved in large slabs; blocks are carved out by a
+// host-side best-fit free list with coalescing.  All users of a block run on the context's compute
+// stream, so a freed block can be handed out again immediately: the next kernel that touches it is
+// ordered after the last one that did.
+struct Arena {
+    struct Slab {
+        char* base;
+        size_t bytes;
+        std::map<size_t, size_t> free_by_off;  // offset -> size
+    };
+    std::vector<Slab> slabs;
+    std::map<void*, std::pair<int, size_t>> live;  // ptr -> (slab, size)
+    size_t in_use = 0, hwm = 0, reserved = 0, limit = 0;
+    int alloc(size_t bytes, void** out);
+    int free(void* p);
+    int release_cached();
+    void destroy();
+};
+
+}  // namespace gcb
+
+struct gcb_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t ev_compute = nullptr, ev_comm = nullptr;
+    gcb::Arena arena;
+    int64_t launches = 0;
+    int gemm_engine = 0;       // 0 auto, 1 simt, 2 tcgen05
+    int last_gemm_engine = 0;
+    int* d_status = nullptr;   // device-side status word written by kernels that give up on a bounded wait
+    void* nccl_comm = nullptr;
+    int dp_rank = 0, dp_world = 1;
+    void* tma_encode = nullptr;  // cuTensorMapEncodeTiled, resolved lazily
+    std::mutex mu;
+};
+
+namespace gcb {
+
+struct Scratch {  // RAII arena block used inside one entry point
+    gcb_ctx* ctx;
+    void* p = nullptr;
+    Scratch(gcb_ctx* c) : ctx(c) {}
+    int get(size_t bytes) { return ctx->arena.alloc(bytes, &p); }
+    ~Scratch() { if (p) ctx->arena.free(p); }
+    template <class T> T* as() { return reinterpret_cast<T*>(p); }
+};
+
+inline int after_launch(gcb_ctx* ctx, const char* what, int n = 1) {
+    ctx->launches += n;
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return cuda_fail(cudaGetLastError(), what);
+    return GCB_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+// streaming variants: data touched once should not evict what the next kernel wants from L2/L1
+__device__ __forceinline__ float4 ld4_stream(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ void st4_stream(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Block-wide sum / max through one shared-memory hop; `red` holds >= 33 floats. Every thread gets the result.
+template <bool IsMax>
+__device__ __forceinline__ float block_reduce(float v, float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = IsMax ? warp_max(v) : warp_sum(v);
+    __syncthreads();  // protect `red` from the previous use
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float r = (lane < nw) ? red[lane] : (IsMax ? -INFINITY : 0.0f);
+    r = IsMax ? warp_max(r) : warp_sum(r);
+    return r;
+}
+#endif
+
+}  // namespace gcb

@@ -1,0 +1,44 @@
+// GEMM entry points: argument validation and engine choice.
+// Reference counterparts: CUDAMath::apply_normal_gemm / apply_batched_gemm (backend/cuda/kernels_math.cu:725-779),
+// whose NMMMeta / BMMMeta fields (core/types.hpp:118-158) map one to one onto the arguments here.
+#include "gemm.cuh"
+
+using namespace gcb;
+
+static int run_gemm(gcb_ctx* ctx, int op_a, int op_b, const GemmArgs& g, const char* who) {
+    GCB_REQUIRE((op_a == GCB_OP_N || op_a == GCB_OP_T) && (op_b == GCB_OP_N || op_b == GCB_OP_T), "%s: op must be GCB_OP_N or GCB_OP_T", who);
+    GCB_REQUIRE(g.M >= 0 && g.N >= 0 && g.K >= 0, "%s: negative dimension", who);
+    if (g.M == 0 || g.N == 0 || g.batch_outer * g.batch_inner == 0) return GCB_OK;
+    GCB_REQUIRE(g.C && (g.K == 0 || (g.A && g.B)), "%s: NULL operand", who);
+    const bool ta = op_a == GCB_OP_T, tb = op_b == GCB_OP_T;
+    GCB_REQUIRE(g.lda >= (ta ? g.M : g.K) && g.ldb >= (tb ? g.K : g.N) && g.ldc >= g.N, "%s: leading dimension smaller than the row length (lda %lld ldb %lld ldc %lld)", who,
+                (long long)g.lda, (long long)g.ldb, (long long)g.ldc);
+    if (ctx->gemm_engine != 1 && gemm_tc_eligible(ta, tb, g)) {
+        int rc = gemm_tc_launch(ctx, ta, tb, g);
+        if (rc != GCB_UNSUPPORTED) return rc;
+    }
+    if (ctx->gemm_engine == 2) {
+        set_error("%s: the tcgen05 engine was forced but cannot take these operands (alignment / leading dimensions)", who);
+        return GCB_UNSUPPORTED;
+    }
+    return gemm_simt_launch(ctx, ta, tb, g);
+}
+
+extern "C" {
+
+int gcb_gemm_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda, const float* B, int64_t ldb, float beta, float* C,
+                 int64_t ldc, const float* bias) {
+    GCB_REQUIRE(ctx, "gcb_gemm_f32: ctx is NULL");
+    GemmArgs g{M, N, K, alpha, beta, A, B, bias, C, lda, ldb, ldc, 0, 0, 0, 0, 0, 0, 1, 1};
+    return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_f32");
+}
+
+int gcb_gemm_batched_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda, int64_t a_so, int64_t a_si, const float* B,
+                         int64_t ldb, int64_t b_so, int64_t b_si, float beta, float* C, int64_t ldc, int64_t c_so, int64_t c_si, int64_t batch_outer, int64_t batch_inner) {
+    GCB_REQUIRE(ctx, "gcb_gemm_batched_f32: ctx is NULL");
+    GCB_REQUIRE(batch_outer >= 0 && batch_inner >= 0, "gcb_gemm_batched_f32: negative batch count");
+    GemmArgs g{M, N, K, alpha, beta, A, B, nullptr, C, lda, ldb, ldc, a_so, a_si, b_so, b_si, c_so, c_si, batch_outer, batch_inner};
+    return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_batched_f32");
+}
+
+}  // extern "C"

@@ -1,0 +1,347 @@
+// Fused LayerNorm / RMSNorm forward and backward (HBM-bound).
+// Reference counterparts: rmsnorm_{forward,backward}_kernel_fast (backend/cuda/kernels_math.cu:787-838,
+// 977-1043) and LayerNormNode's chain of ~27 generic dispatches (graph/nodes/normalization_nodes.hpp:24-134).
+//
+// Fast path (cols % 4 == 0, cols <= 1024, 16-byte aligned rows): one warp owns a whole row in registers
+// (lane l holds float4 chunks l, l+32, ...), so every row statistic is a pair of warp-shuffle reductions and
+// x / dy are read exactly once.  In the backward the warp also keeps its gamma and its running dgamma / dbeta
+// column sums in registers across all the rows it visits; the per-warp sums are combined through shared memory
+// into one partial per CTA and a second tiny kernel adds the CTA partials in a fixed order (no atomics, so the
+// result is deterministic).  Other shapes take a CTA-per-row kernel with the same arithmetic.
+#include "common.cuh"
+
+namespace gcb {
+
+constexpr int kNormWarps = 4;  // warps per CTA on the fast path
+
+template <int NCHUNK, bool IS_LN>
+__global__ void __launch_bounds__(kNormWarps * 32) norm_fwd_warp(float* __restrict__ y, float* __restrict__ stat0, float* __restrict__ stat1, const float* __restrict__ x,
+                                                                 const float* __restrict__ gamma, const float* __restrict__ beta, int64_t rows, int cols, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * kNormWarps + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kNormWarps;
+    const float inv_c = 1.0f / (float)cols;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const float* xr = x + r * cols;
+        float4 v[NCHUNK];
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < NCHUNK; ++k) {
+            const int c = (lane + 32 * k) * 4;
+            v[k] = (c < cols) ? ld4_stream(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            s += IS_LN ? (v[k].x + v[k].y + v[k].z + v[k].w) : (v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w);
+        }
+        s = warp_sum(s);
+        float mu = 0.0f, rs;
+        if (IS_LN) {
+            mu = s * inv_c;
+            float q = 0.0f;
+#pragma unroll
+            for (int k = 0; k < NCHUNK; ++k) {
+                const int c = (lane + 32 * k) * 4;
+                if (c < cols) {
+                    const float a = v[k].x - mu, b = v[k].y - mu, d = v[k].z - mu, e = v[k].w - mu;
+                    q += a * a + b * b + d * d + e * e;
+                }
+            }
+            q = warp_sum(q);
+            rs = 1.0f / sqrtf(q * inv_c + eps);
+        } else {
+            rs = 1.0f / sqrtf(s * inv_c + eps);
+        }
+        if (lane == 0) {
+            if (IS_LN) { if (stat0) stat0[r] = mu; if (stat1) stat1[r] = rs; }
+            else if (stat0) stat0[r] = rs;
+        }
+        float* yr = y + r * cols;
+#pragma unroll
+        for (int k = 0; k < NCHUNK; ++k) {
+            const int c = (lane + 32 * k) * 4;
+            if (c < cols) {
+                const float4 g = __ldg(reinterpret_cast<const float4*>(gamma + c));
+                float4 o;
+                if (IS_LN) {
+                    const float4 b = __ldg(reinterpret_cast<const float4*>(beta + c));
+                    o = make_float4((v[k].x - mu) * rs * g.x + b.x, (v[k].y - mu) * rs * g.y + b.y, (v[k].z - mu) * rs * g.z + b.z, (v[k].w - mu) * rs * g.w + b.w);
+                } else {
+                    o = make_float4(v[k].x * rs * g.x, v[k].y * rs * g.y, v[k].z * rs * g.z, v[k].w * rs * g.w);
+                }
+                st4(yr + c, o);
+            }
+        }
+    }
+}
+
+// partial layout: [gridDim.x][2][cols] (dgamma sums, then dbeta sums; RMSNorm leaves the second half unused)
+template <int NCHUNK, bool IS_LN>
+__global__ void __launch_bounds__(kNormWarps * 32) norm_bwd_warp(float* __restrict__ dx, float* __restrict__ partial, const float* __restrict__ dy, const float* __restrict__ x,
+                                                                 const float* __restrict__ gamma, const float* __restrict__ stat0, const float* __restrict__ stat1,
+                                                                 int64_t rows, int cols, int acc_dx, int want_params) {
+    extern __shared__ float sm[];  // [kNormWarps][2][cols]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t warp = (int64_t)blockIdx.x * kNormWarps + wid;
+    const int64_t nwarps = (int64_t)gridDim.x * kNormWarps;
+    const float inv_c = 1.0f / (float)cols;
+    float4 g4[NCHUNK], dg[NCHUNK], db[NCHUNK];
+#pragma unroll
+    for (int k = 0; k < NCHUNK; ++k) {
+        const int c = (lane + 32 * k) * 4;
+        g4[k] = (c < cols) ? __ldg(reinterpret_cast<const float4*>(gamma + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        dg[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        db[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const float* xr = x + r * cols;
+        const float* dr = dy + r * cols;
+        float4 xv[NCHUNK], dv[NCHUNK];
+#pragma unroll
+        for (int k = 0; k < NCHUNK; ++k) {
+            const int c = (lane + 32 * k) * 4;
+            if (c < cols) { xv[k] = ld4_stream(xr + c); dv[k] = ld4_stream(dr + c); }
+            else { xv[k] = make_float4(0.f, 0.f, 0.f, 0.f); dv[k] = xv[k]; }
+        }
+        const float mu = IS_LN ? stat0[r] : 0.0f;
+        const float rs = IS_LN ? stat1[r] : stat0[r];
+        float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < NCHUNK; ++k) {
+            // xv becomes xhat, and the lane's dgamma / dbeta column sums advance
+            xv[k].x = (xv[k].x - mu) * rs; xv[k].y = (xv[k].y - mu) * rs; xv[k].z = (xv[k].z - mu) * rs; xv[k].w = (xv[k].w - mu) * rs;
+            dg[k].x += dv[k].x * xv[k].x; dg[k].y += dv[k].y * xv[k].y; dg[k].z += dv[k].z * xv[k].z; dg[k].w += dv[k].w * xv[k].w;
+            if (IS_LN) { db[k].x += dv[k].x; db[k].y += dv[k].y; db[k].z += dv[k].z; db[k].w += dv[k].w; }
+            // dv becomes g = dy * gamma
+            dv[k].x *= g4[k].x; dv[k].y *= g4[k].y; dv[k].z *= g4[k].z; dv[k].w *= g4[k].w;
+            if (IS_LN) s1 += dv[k].x + dv[k].y + dv[k].z + dv[k].w;
+            s2 += dv[k].x * xv[k].x + dv[k].y * xv[k].y + dv[k].z * xv[k].z + dv[k].w * xv[k].w;
+        }
+        if (dx != nullptr) {
+            if (IS_LN) s1 = warp_sum(s1);
+            s2 = warp_sum(s2);
+            const float m1 = s1 * inv_c, m2 = s2 * inv_c;
+            float* or_ = dx + r * cols;
+#pragma unroll
+            for (int k = 0; k < NCHUNK; ++k) {
+                const int c = (lane + 32 * k) * 4;
+                if (c < cols) {
+                    float4 o = make_float4(rs * (dv[k].x - m1 - xv[k].x * m2), rs * (dv[k].y - m1 - xv[k].y * m2), rs * (dv[k].z - m1 - xv[k].z * m2), rs * (dv[k].w - m1 - xv[k].w * m2));
+                    if (acc_dx) { const float4 old = ld4(or_ + c); o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+                    st4(or_ + c, o);
+                }
+            }
+        }
+    }
+    if (!want_params) return;
+    float* mine = sm + (size_t)wid * 2 * cols;
+#pragma unroll
+    for (int k = 0; k < NCHUNK; ++k) {
+        const int c = (lane + 32 * k) * 4;
+        if (c < cols) { st4(mine + c, dg[k]); st4(mine + cols + c, db[k]); }
+    }
+    __syncthreads();
+    float* outp = partial + (size_t)blockIdx.x * 2 * cols;
+    for (int i = threadIdx.x; i < 2 * cols; i += kNormWarps * 32) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kNormWarps; ++w) s += sm[(size_t)w * 2 * cols + i];
+        outp[i] = s;
+    }
+}
+
+__global__ void __launch_bounds__(256) norm_params_stage2(float* __restrict__ dgamma, float* __restrict__ dbeta, const float* __restrict__ partial, int nparts, int cols, int accumulate) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;  // over 2 * cols
+    if (i >= 2 * cols) return;
+    float* dst = (i < cols) ? dgamma : dbeta;
+    if (dst == nullptr) return;
+    float s = 0.0f;
+    for (int k = 0; k < nparts; ++k) s += partial[(size_t)k * 2 * cols + i];
+    const int c = (i < cols) ? i : i - cols;
+    dst[c] = accumulate ? dst[c] + s : s;
+}
+
+// ---- generic shapes: CTA per row ---------------------------------------------------------------
+template <bool IS_LN>
+__global__ void __launch_bounds__(256) norm_fwd_block(float* __restrict__ y, float* __restrict__ stat0, float* __restrict__ stat1, const float* __restrict__ x,
+                                                      const float* __restrict__ gamma, const float* __restrict__ beta, int64_t rows, int64_t cols, float eps) {
+    __shared__ float red[33];
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float* xr = x + r * cols;
+        float s = 0.0f;
+        for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += IS_LN ? xr[c] : xr[c] * xr[c];
+        s = block_reduce<false>(s, red);
+        float mu = 0.0f, rs;
+        if (IS_LN) {
+            mu = s / (float)cols;
+            float q = 0.0f;
+            for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) { const float d = xr[c] - mu; q += d * d; }
+            q = block_reduce<false>(q, red);
+            rs = 1.0f / sqrtf(q / (float)cols + eps);
+        } else {
+            rs = 1.0f / sqrtf(s / (float)cols + eps);
+        }
+        if (threadIdx.x == 0) {
+            if (IS_LN) { if (stat0) stat0[r] = mu; if (stat1) stat1[r] = rs; }
+            else if (stat0) stat0[r] = rs;
+        }
+        for (int64_t c = threadIdx.x; c < cols; c += blockDim.x)
+            y[r * cols + c] = IS_LN ? (xr[c] - mu) * rs * gamma[c] + beta[c] : xr[c] * rs * gamma[c];
+    }
+}
+template <bool IS_LN>
+__global__ void __launch_bounds__(256) norm_bwd_dx_block(float* __restrict__ dx, const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
+                                                         const float* __restrict__ stat0, const float* __restrict__ stat1, int64_t rows, int64_t cols, int acc_dx) {
+    __shared__ float red[33];
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float mu = IS_LN ? stat0[r] : 0.0f, rs = IS_LN ? stat1[r] : stat0[r];
+        float s1 = 0.0f, s2 = 0.0f;
+        for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float g = dy[r * cols + c] * gamma[c], xh = (x[r * cols + c] - mu) * rs;
+            s1 += g;
+            s2 += g * xh;
+        }
+        s1 = IS_LN ? block_reduce<false>(s1, red) : 0.0f;
+        s2 = block_reduce<false>(s2, red);
+        const float m1 = s1 / (float)cols, m2 = s2 / (float)cols;
+        for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float g = dy[r * cols + c] * gamma[c], xh = (x[r * cols + c] - mu) * rs;
+            const float o = rs * (g - m1 - xh * m2);
+            dx[r * cols + c] = acc_dx ? dx[r * cols + c] + o : o;
+        }
+    }
+}
+// column sums for generic shapes: block = 32 columns x 8 row lanes, grid.y slabs of rows; partial [slabs][2][cols]
+template <bool IS_LN>
+__global__ void __launch_bounds__(256) norm_bwd_params_block(float* __restrict__ partial, const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ stat0,
+                                                             const float* __restrict__ stat1, int64_t rows, int64_t cols, int64_t rows_per_slab) {
+    __shared__ float sg[8][33], sb[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t c = (int64_t)blockIdx.x * 32 + tx;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_slab, r1 = min(rows, r0 + rows_per_slab);
+    float ag = 0.0f, ab = 0.0f;
+    if (c < cols) {
+        for (int64_t r = r0 + ty; r < r1; r += 8) {
+            const float mu = IS_LN ? stat0[r] : 0.0f, rs = IS_LN ? stat1[r] : stat0[r];
+            const float d = dy[r * cols + c];
+            ag += d * (x[r * cols + c] - mu) * rs;
+            ab += d;
+        }
+    }
+    sg[ty][tx] = ag; sb[ty][tx] = ab;
+    __syncthreads();
+    if (ty == 0 && c < cols) {
+        float a = 0.0f, b = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { a += sg[j][tx]; b += sb[j][tx]; }
+        partial[(size_t)blockIdx.y * 2 * cols + c] = a;
+        partial[(size_t)blockIdx.y * 2 * cols + cols + c] = b;
+    }
+}
+
+static int pick_chunks(int64_t cols) {
+    if (cols <= 128) return 1;
+    if (cols <= 256) return 2;
+    if (cols <= 512) return 4;
+    if (cols <= 768) return 6;
+    return 8;
+}
+
+template <bool IS_LN>
+static int norm_fwd(gcb_ctx* ctx, float* y, float* s0, float* s1, const float* x, const float* gamma, const float* beta, int64_t rows, int64_t cols, float eps) {
+    if (rows == 0 || cols == 0) return GCB_OK;
+    cudaSetDevice(ctx->device);
+    const bool fast = cols % 4 == 0 && cols <= 1024 && aligned16(x) && aligned16(y) && aligned16(gamma) && (!IS_LN || aligned16(beta));
+    if (fast) {
+        int64_t blocks = std::min<int64_t>((rows + kNormWarps - 1) / kNormWarps, (int64_t)kSMs * 8);
+        const int n = pick_chunks(cols);
+#define GCB_FWD(N) norm_fwd_warp<N, IS_LN><<<(unsigned)blocks, kNormWarps * 32, 0, ctx->stream>>>(y, s0, s1, x, gamma, beta, rows, (int)cols, eps)
+        if (n == 1) GCB_FWD(1); else if (n == 2) GCB_FWD(2); else if (n == 4) GCB_FWD(4); else if (n == 6) GCB_FWD(6); else GCB_FWD(8);
+#undef GCB_FWD
+    } else {
+        int64_t blocks = std::min<int64_t>(rows, (int64_t)kSMs * 8);
+        norm_fwd_block<IS_LN><<<(unsigned)blocks, 256, 0, ctx->stream>>>(y, s0, s1, x, gamma, beta, rows, cols, eps);
+    }
+    return after_launch(ctx, IS_LN ? "layernorm_fwd" : "rmsnorm_fwd");
+}
+
+template <bool IS_LN>
+static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const float* dy, const float* x, const float* gamma, const float* s0, const float* s1,
+                    int64_t rows, int64_t cols, int acc_dx, int acc_params) {
+    if (cols == 0) return GCB_OK;
+    cudaSetDevice(ctx->device);
+    const bool want_params = dgamma != nullptr || dbeta != nullptr;
+    if (rows == 0) {
+        if (want_params && !acc_params) {
+            if (dgamma) { int rc = gcb_fill_f32(ctx, dgamma, 0.0f, cols); if (rc) return rc; }
+            if (dbeta) { int rc = gcb_fill_f32(ctx, dbeta, 0.0f, cols); if (rc) return rc; }
+        }
+        return GCB_OK;
+    }
+    const bool fast = cols % 4 == 0 && cols <= 1024 && aligned16(x) && aligned16(dy) && aligned16(gamma) && (dx == nullptr || aligned16(dx));
+    const char* name = IS_LN ? "layernorm_bwd" : "rmsnorm_bwd";
+    if (fast) {
+        // 3 CTAs of 4 warps per SM: ~170 registers per thread, 96 KB of row data in flight per SM
+        int64_t blocks = std::min<int64_t>((rows + kNormWarps - 1) / kNormWarps, (int64_t)kSMs * 3);
+        Scratch sc(ctx);
+        if (want_params) { int rc = sc.get(sizeof(float) * blocks * 2 * cols); if (rc) return rc; }
+        const size_t smem = want_params ? sizeof(float) * kNormWarps * 2 * cols : 0;
+        const int n = pick_chunks(cols);
+#define GCB_BWD(N) norm_bwd_warp<N, IS_LN><<<(unsigned)blocks, kNormWarps * 32, smem, ctx->stream>>>(dx, sc.as<float>(), dy, x, gamma, s0, s1, rows, (int)cols, acc_dx, want_params ? 1 : 0)
+        if (n == 1) GCB_BWD(1); else if (n == 2) GCB_BWD(2); else if (n == 4) GCB_BWD(4); else if (n == 6) GCB_BWD(6); else GCB_BWD(8);
+#undef GCB_BWD
+        int rc = after_launch(ctx, name);
+        if (rc) return rc;
+        if (want_params) {
+            norm_params_stage2<<<(unsigned)((2 * cols + 255) / 256), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params);
+            rc = after_launch(ctx, name);
+        }
+        return rc;
+    }
+    if (dx) {
+        int64_t blocks = std::min<int64_t>(rows, (int64_t)kSMs * 8);
+        norm_bwd_dx_block<IS_LN><<<(unsigned)blocks, 256, 0, ctx->stream>>>(dx, dy, x, gamma, s0, s1, rows, cols, acc_dx);
+        int rc = after_launch(ctx, name);
+        if (rc) return rc;
+    }
+    if (want_params) {
+        GCB_REQUIRE(cols < (1 << 30), "%s: too many columns", name);
+        const int64_t col_tiles = (cols + 31) / 32;
+        int64_t slabs = std::max<int64_t>(1, std::min<int64_t>((int64_t)kSMs * 4 / col_tiles, (rows + 63) / 64));
+        const int64_t rps = (rows + slabs - 1) / slabs;
+        slabs = (rows + rps - 1) / rps;
+        Scratch sc(ctx);
+        int rc = sc.get(sizeof(float) * slabs * 2 * cols);
+        if (rc) return rc;
+        dim3 grid((unsigned)col_tiles, (unsigned)slabs);
+        norm_bwd_params_block<IS_LN><<<grid, 256, 0, ctx->stream>>>(sc.as<float>(), dy, x, s0, s1, rows, cols, rps);
+        rc = after_launch(ctx, name);
+        if (rc) return rc;
+        norm_params_stage2<<<(unsigned)((2 * cols + 255) / 256), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)slabs, (int)cols, acc_params);
+        return after_launch(ctx, name);
+    }
+    return GCB_OK;
+}
+
+}  // namespace gcb
+
+using namespace gcb;
+
+extern "C" {
+
+int gcb_rmsnorm_fwd_f32(gcb_ctx* ctx, float* y, float* inv_rms, const float* x, const float* gamma, int64_t rows, int64_t cols, float eps) {
+    GCB_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (y && x && gamma)), "gcb_rmsnorm_fwd_f32: bad arguments");
+    return norm_fwd<false>(ctx, y, inv_rms, nullptr, x, gamma, nullptr, rows, cols, eps);
+}
+int gcb_rmsnorm_bwd_f32(gcb_ctx* ctx, float* dx, float* dgamma, const float* dy, const float* x, const float* gamma, const float* inv_rms, int64_t rows, int64_t cols, int acc_dx, int acc_dgamma) {
+    GCB_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (dy && x && gamma && inv_rms)), "gcb_rmsnorm_bwd_f32: bad arguments");
+    return norm_bwd<false>(ctx, dx, dgamma, nullptr, dy, x, gamma, inv_rms, nullptr, rows, cols, acc_dx, acc_dgamma);
+}
+int gcb_layernorm_fwd_f32(gcb_ctx* ctx, float* y, float* mean, float* rstd, const float* x, const float* gamma, const float* beta, int64_t rows, int64_t cols, float eps) {
+    GCB_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (y && x && gamma && beta)), "gcb_layernorm_fwd_f32: bad arguments");
+    return norm_fwd<true>(ctx, y, mean, rstd, x, gamma, beta, rows, cols, eps);
+}
+int gcb_layernorm_bwd_f32(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const float* dy, const float* x, const float* gamma, const float* mean, const float* rstd,
+                          int64_t rows, int64_t cols, int acc_dx, int acc_params) {
+    GCB_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (dy && x && gamma && mean && rstd)), "gcb_layernorm_bwd_f32: bad arguments");
+    return norm_bwd<true>(ctx, dx, dgamma, dbeta, dy, x, gamma, mean, rstd, rows, cols, acc_dx, acc_params);
+}
+
+}  // extern "C"

@@ -1,0 +1,195 @@
+/*
+ * gradc_b200 — C ABI of the sm_100a backend for GradCraft's training hot path.
+ *
+ * Every entry point replaces one member of the reference's CUDA backend surface
+ * (class CUDAMath, gradc/backend/cuda/cuda_math.hpp:7-60; class CUDAUtils,
+ * gradc/backend/cuda/cuda_utils.hpp:6-22; class CUDAMemPool, gradc/backend/cuda/memory_pool.hpp:13-103)
+ * that gradc/backend/dispatcher.hpp:43-256 forwards to.  The citation beside each declaration names
+ * the reference interface it stands in for.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; all device pointers are fp32 unless the name says otherwise;
+ *   - the caller owns every buffer; a NULL optional output means "skip";
+ *   - `accumulate != 0` means "+= into an existing gradient" (the reference's acc_* flags);
+ *   - calls are asynchronous and ordered on the context's compute stream;
+ *   - every call returns a gcb_status; gcb_last_error_string() describes the last failure of the
+ *     calling thread.  There is no CPU fallback: without a CUDA device every call fails.
+ */
+#ifndef GRADC_B200_H
+#define GRADC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define GCB_API __attribute__((visibility("default")))
+#else
+#define GCB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gcb_ctx gcb_ctx;
+
+typedef enum gcb_status {
+    GCB_OK = 0,
+    GCB_INVALID_ARG = 1,
+    GCB_UNSUPPORTED = 2,
+    GCB_OOM = 3,
+    GCB_CUDA_ERROR = 4,
+    GCB_NCCL_ERROR = 5,
+    GCB_TIMEOUT = 6
+} gcb_status;
+
+/* Mirrors gradc/backend/op_types.hpp:3-6 (only the members the training step dispatches). */
+typedef enum gcb_unary_op { GCB_U_IDENTITY = 0, GCB_U_NEG = 1, GCB_U_SQUARE = 2, GCB_U_SQRT = 3, GCB_U_GELU = 4, GCB_U_SILU = 5, GCB_U_EXP = 6, GCB_U_LOG = 7, GCB_U_RELU = 8, GCB_U_SIGMOID = 9, GCB_U_TANH = 10 } gcb_unary_op;
+typedef enum gcb_binary_op { GCB_B_ADD = 0, GCB_B_SUB = 1, GCB_B_MUL = 2, GCB_B_DIV = 3, GCB_B_BGELU = 4, GCB_B_ISUB = 5, GCB_B_IDIV = 6 } gcb_binary_op;
+typedef enum gcb_index_type { GCB_IDX_I64 = 0, GCB_IDX_I32 = 1 } gcb_index_type;
+typedef enum gcb_gemm_op { GCB_OP_N = 0, GCB_OP_T = 1 } gcb_gemm_op; /* MatrixTensorOp, gradc/core/types.hpp:113-116 */
+
+/* ---- context, streams, errors ------------------------------------------------------------------ */
+GCB_API const char* gcb_last_error_string(void);
+/* One context per device: compute stream + arena (+ NCCL communicator once gcb_dp_init ran).
+ * Replaces the implicit "cudaSetDevice(index); launch on stream 0" of every CUDAMath::apply_*. */
+GCB_API int gcb_ctx_create(int device, gcb_ctx** out);
+/* Same, but every kernel is issued on an existing cudaStream_t (passed as void*). */
+GCB_API int gcb_ctx_create_on_stream(int device, void* cuda_stream, gcb_ctx** out);
+GCB_API int gcb_ctx_destroy(gcb_ctx* ctx);
+GCB_API void* gcb_ctx_stream(gcb_ctx* ctx);
+GCB_API int gcb_ctx_device(gcb_ctx* ctx);
+GCB_API int gcb_ctx_sync(gcb_ctx* ctx); /* cudaStreamSynchronize + sticky-error check */
+/* Number of kernels this library launched through ctx since creation. */
+GCB_API int64_t gcb_ctx_launch_count(gcb_ctx* ctx);
+/* Which GEMM engine ran last: 0 none, 1 SIMT fp32, 2 tcgen05 3xTF32. */
+GCB_API int gcb_ctx_last_gemm_engine(gcb_ctx* ctx);
+/* Force the GEMM engine: 0 auto, 1 SIMT fp32 only, 2 tcgen05 only (fails where it cannot run). */
+GCB_API int gcb_ctx_set_gemm_engine(gcb_ctx* ctx, int engine);
+
+/* ---- arena: CUDAMemPool::{allocate,free,clear,get_hwm_gb}, memory_pool.hpp:40-102 -------------- */
+GCB_API int gcb_arena_alloc(gcb_ctx* ctx, size_t bytes, void** out);
+GCB_API int gcb_arena_free(gcb_ctx* ctx, void* ptr);
+GCB_API int gcb_arena_release_cached(gcb_ctx* ctx);           /* CUDAMemPool::clear */
+GCB_API size_t gcb_arena_high_water_bytes(gcb_ctx* ctx);      /* CUDAMemPool::get_hwm_gb */
+GCB_API size_t gcb_arena_in_use_bytes(gcb_ctx* ctx);
+GCB_API size_t gcb_arena_reserved_bytes(gcb_ctx* ctx);
+/* Test hook: refuse to grow the arena beyond `bytes` (0 = no limit) so OOM handling can be exercised
+ * on the host without exhausting a shared GPU. */
+GCB_API int gcb_arena_set_limit(gcb_ctx* ctx, size_t bytes);
+
+/* ---- copies: Storage ctor / ToNode / Tensor::item, core/storage.hpp:64-68, memory_nodes.hpp:212-317 */
+GCB_API int gcb_copy_h2d(gcb_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);        /* synchronous */
+GCB_API int gcb_copy_d2h(gcb_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);        /* synchronous */
+GCB_API int gcb_copy_h2d_async(gcb_ctx* ctx, void* dst_dev, const void* src_pinned, size_t bytes); /* on the compute stream */
+GCB_API int gcb_copy_d2h_async(gcb_ctx* ctx, void* dst_pinned, const void* src_dev, size_t bytes);
+GCB_API int gcb_copy_d2d(gcb_ctx* ctx, void* dst, const void* src, size_t bytes);
+GCB_API int gcb_host_alloc_pinned(size_t bytes, void** out);
+GCB_API int gcb_host_free_pinned(void* ptr);
+
+/* ---- fills: CUDAUtils::{fill,fill_arange,set_scalar}, cuda_utils.hpp:8-14 ----------------------- */
+GCB_API int gcb_fill_f32(gcb_ctx* ctx, float* ptr, float value, int64_t n);
+GCB_API int gcb_fill_arange_i64(gcb_ctx* ctx, int64_t* ptr, int64_t start, int64_t step, int64_t n);
+GCB_API int gcb_set_scalar_f32(gcb_ctx* ctx, float* ptr, float value);
+
+/* ---- elementwise: CUDAMath::apply_{unary,binary}_{out_of_place,in_place}, cuda_math.hpp:9-18 ---- */
+/* dense, same-shape operands */
+GCB_API int gcb_unary_f32(gcb_ctx* ctx, int op, float* out, const float* in, int64_t n);
+GCB_API int gcb_binary_f32(gcb_ctx* ctx, int op, float* out, const float* a, const float* b, int64_t n);
+/* b is a single device scalar broadcast over a (the reference's 1-element tensors) */
+GCB_API int gcb_binary_scalar_f32(gcb_ctx* ctx, int op, float* out, const float* a, float b, int64_t n);
+/* out[r, c] = a[r, c] op b[c]: bias-style broadcast of a trailing vector over `rows` rows */
+GCB_API int gcb_binary_rowvec_f32(gcb_ctx* ctx, int op, float* out, const float* a, const float* vec, int64_t rows, int64_t cols);
+/* general strided/broadcast form (<= 8 dims; stride 0 broadcasts), element strides */
+GCB_API int gcb_binary_strided_f32(gcb_ctx* ctx, int op, int ndim, const int64_t* shape, float* out, const int64_t* out_strides,
+                           const float* a, const int64_t* a_strides, const float* b, const int64_t* b_strides);
+/* strided copy: ContiguousNode / permute copies (UnaryOp::Identity on views) */
+GCB_API int gcb_copy_strided_f32(gcb_ctx* ctx, int ndim, const int64_t* shape, float* out, const int64_t* out_strides,
+                         const float* in, const int64_t* in_strides, int accumulate);
+
+/* ---- reductions: CUDAMath::apply_reduction_operation, cuda_math.hpp:19-20 ---------------------- */
+/* out[c] (+)= sum_r in[r, c]: bias gradients / unbroadcast_grad (core/detail/tensor_detail.hpp:15-33);
+ * rows are grouped as [outer, inner, cols] and summed over `outer` only when inner > 1
+ * (positional-embedding gradient: B x T x C -> T x C).  Deterministic two-stage reduction. */
+GCB_API int gcb_reduce_rows_f32(gcb_ctx* ctx, float* out, const float* in, int64_t outer, int64_t inner_cols, int accumulate);
+/* *out (+)= sum in[i]^2 — reduction_kernel_whole as used by GlobalNormClipper (norm_clip.hpp:24-38) */
+GCB_API int gcb_sum_squares_f32(gcb_ctx* ctx, float* out_scalar, const float* in, int64_t n, int accumulate);
+
+/* ---- GEMM: CUDAMath::apply_normal_gemm / apply_batched_gemm, cuda_math.hpp:23-28 ---------------
+ * Row-major C[M,N] = alpha * op(A)[M,K] * op(B)[K,N] + beta * C, leading dimensions in elements,
+ * exactly the fields of NMMMeta / BMMMeta (gradc/core/types.hpp:118-158).
+ * bias (optional, length N) is added to every row — it folds the AddNode that follows each Linear
+ * matmul (nn/layers/linear.hpp:23).  fp32 accuracy: tcgen05 kind::tf32 issued three times on
+ * split operands (3xTF32) or the SIMT fp32 engine for shapes TMA cannot address. */
+GCB_API int gcb_gemm_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda,
+                 const float* B, int64_t ldb, float beta, float* C, int64_t ldc, const float* bias);
+/* Batched with two-level batch strides (batch index = outer * batch_inner + inner) so that head-sliced
+ * (B, T, H, D) views are consumed in place instead of through contiguous() copies. */
+GCB_API int gcb_gemm_batched_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha,
+                         const float* A, int64_t lda, int64_t a_stride_outer, int64_t a_stride_inner,
+                         const float* B, int64_t ldb, int64_t b_stride_outer, int64_t b_stride_inner,
+                         float beta, float* C, int64_t ldc, int64_t c_stride_outer, int64_t c_stride_inner,
+                         int64_t batch_outer, int64_t batch_inner);
+
+/* ---- embedding: CUDAMath::apply_embed / apply_scatter_add, cuda_math.hpp:29-32 ------------------ */
+GCB_API int gcb_embed_f32(gcb_ctx* ctx, float* out, const void* indices, int index_type, const float* table, int64_t n_indices, int64_t width, int64_t vocab);
+/* dtable[idx[i], :] += dy[i, :].  Deterministic: positions are counting-sorted by row (stable) and each
+ * row is accumulated in ascending position order.  Out-of-range indices are reported, not dereferenced. */
+GCB_API int gcb_scatter_add_f32(gcb_ctx* ctx, float* dtable, const void* indices, int index_type, const float* dy, int64_t n_indices, int64_t width, int64_t vocab);
+/* The integer plan of the scatter alone (for bit-exact bookkeeping checks): order[n] = positions sorted
+ * by row (stable), counts[vocab], offsets[vocab + 1].  All int32 device buffers. */
+GCB_API int gcb_scatter_plan_i32(gcb_ctx* ctx, int32_t* order, int32_t* counts, int32_t* offsets, const void* indices, int index_type, int64_t n_indices, int64_t vocab);
+
+/* ---- normalisation: apply_rmsnorm_{forward,backward}, cuda_math.hpp:33-38; LayerNormNode,
+ *      graph/nodes/normalization_nodes.hpp:24-134 (a chain of ~27 dispatches in the reference) ------ */
+GCB_API int gcb_rmsnorm_fwd_f32(gcb_ctx* ctx, float* y, float* inv_rms /*opt*/, const float* x, const float* gamma, int64_t rows, int64_t cols, float eps);
+GCB_API int gcb_rmsnorm_bwd_f32(gcb_ctx* ctx, float* dx /*opt*/, float* dgamma /*opt*/, const float* dy, const float* x, const float* gamma, const float* inv_rms,
+                        int64_t rows, int64_t cols, int accumulate_dx, int accumulate_dgamma);
+GCB_API int gcb_layernorm_fwd_f32(gcb_ctx* ctx, float* y, float* mean /*opt*/, float* rstd /*opt*/, const float* x, const float* gamma, const float* beta,
+                          int64_t rows, int64_t cols, float eps);
+GCB_API int gcb_layernorm_bwd_f32(gcb_ctx* ctx, float* dx /*opt*/, float* dgamma /*opt*/, float* dbeta /*opt*/, const float* dy, const float* x, const float* gamma,
+                          const float* mean, const float* rstd, int64_t rows, int64_t cols, int accumulate_dx, int accumulate_dparams);
+
+/* ---- activations: GeLUNode + BGeLU (activation_nodes.hpp:157-192, math_functors.cuh:184-214);
+ *      apply_swiglu_{forward,backward}, cuda_math.hpp:51-56 ------------------------------------------ */
+GCB_API int gcb_gelu_fwd_f32(gcb_ctx* ctx, float* y, const float* x, int64_t n);
+GCB_API int gcb_gelu_bwd_f32(gcb_ctx* ctx, float* dx, const float* dy, const float* x, int64_t n, int accumulate);
+GCB_API int gcb_swiglu_fwd_f32(gcb_ctx* ctx, float* out, const float* a, const float* b, int64_t n);
+GCB_API int gcb_swiglu_bwd_f32(gcb_ctx* ctx, float* da /*opt*/, float* db /*opt*/, const float* dy, const float* a, const float* b, int64_t n, int acc_a, int acc_b);
+
+/* ---- attention softmax: apply_causal_softmax_{forward,backward}, cuda_math.hpp:39-44 ------------ */
+/* rows = B*H*T rows of length T; row r belongs to query position r % T.  In-place allowed. */
+GCB_API int gcb_causal_softmax_fwd_f32(gcb_ctx* ctx, float* probs, const float* scores, float scale, int64_t rows, int64_t seq_len);
+GCB_API int gcb_causal_softmax_bwd_f32(gcb_ctx* ctx, float* dscores, const float* dprobs, const float* probs, float scale, int64_t rows, int64_t seq_len, int accumulate);
+
+/* ---- loss: apply_sparse_softmax_crossentropy_{forward,backward}, cuda_math.hpp:45-50 ------------ */
+/* probs may alias logits.  *loss = mean_r(-log(p[r, t_r] + eps)), reduced in a fixed order. */
+GCB_API int gcb_softmax_ce_fwd_f32(gcb_ctx* ctx, float* loss_scalar, float* probs, const float* logits, const void* targets, int index_type, int64_t rows, int64_t vocab, float eps);
+/* dlogits = (p - onehot(t)) * upstream / rows; dlogits may alias probs; upstream passed by value. */
+GCB_API int gcb_softmax_ce_bwd_f32(gcb_ctx* ctx, float* dlogits, const float* probs, const void* targets, int index_type, float upstream, int64_t rows, int64_t vocab, int accumulate);
+
+/* ---- optimizer: apply_adamw_step, cuda_math.hpp:57-59; AdamW::step, nn/optim/adam.hpp:41-55 ------ */
+/* beta1_pow / beta2_pow are beta^t already advanced for this step.  grad_scale multiplies the gradient
+ * first (the clip factor of GlobalNormClipper, norm_clip.hpp:42-55; pass 1 for none). */
+GCB_API int gcb_adamw_step_f32(gcb_ctx* ctx, float* w, float* m, float* v, const float* grad, int64_t n, float lr, float beta1, float beta2,
+                       float beta1_pow, float beta2_pow, float weight_decay, float eps, int no_decay, float grad_scale);
+/* One launch over a whole parameter arena: w/m/v/grad are parallel arrays of `n` floats laid out in chunks
+ * of GCB_ADAMW_CHUNK elements; decay_mask[chunk] != 0 applies weight decay to that chunk. */
+#define GCB_ADAMW_CHUNK 1024
+GCB_API int gcb_adamw_arena_f32(gcb_ctx* ctx, float* w, float* m, float* v, const float* grad, const uint8_t* decay_mask, int64_t n, float lr, float beta1,
+                        float beta2, float beta1_pow, float beta2_pow, float weight_decay, float eps, float grad_scale);
+
+/* ---- data parallel (no counterpart in the reference, which is single-GPU) ----------------------- */
+#define GCB_DP_ID_BYTES 128
+GCB_API int gcb_dp_unique_id(uint8_t id[GCB_DP_ID_BYTES]);
+GCB_API int gcb_dp_init(gcb_ctx* ctx, const uint8_t id[GCB_DP_ID_BYTES], int rank, int world);
+/* average-allreduce of grads[offset .. offset+n) on the communication stream after the work already
+ * queued on the compute stream; consumers call gcb_dp_wait. */
+GCB_API int gcb_dp_allreduce_avg_f32(gcb_ctx* ctx, float* buf, int64_t n);
+GCB_API int gcb_dp_wait(gcb_ctx* ctx);
+GCB_API int gcb_dp_finalize(gcb_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRADC_B200_H */
