@@ -113,7 +113,7 @@ class Context:
         self.h = h
 
     def __getattr__(self, name):
-        fn = getattr(self.lib, name)
+        fn = getattr(self.lib, name, None) or getattr(self.lib, "ctx_" + name)
         return lambda *a: fn(self.h, *a)
 
     def close(self):
