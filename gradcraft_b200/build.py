@@ -50,7 +50,27 @@ def build(verbose=False, force=False):
             raise RuntimeError("link failed:\n" + r.stderr[-4000:])
         if verbose:
             print("linked", LIB)
+    build_trainer(verbose, force or bool(jobs))
     return LIB
+
+
+TRAINER_SRC = os.path.join(CSRC, "host", "trainer.cpp")
+TRAINER_LIB = os.path.join(HERE, "libgradc_trainer.so")
+
+
+def build_trainer(verbose=False, force=False):
+    """Host-side C++ (the gradc API mirror + the training step) into libgradc_trainer.so, linked against the kernel library."""
+    hdrs = tuple(os.path.join(HERE, "gradc", f) for f in os.listdir(os.path.join(HERE, "gradc"))) + (os.path.join(HERE, "..", "include", "gradc_trainer.h"), os.path.join(HERE, "..", "include", "gradc_b200.h"))
+    if not (force or _newer(TRAINER_SRC, TRAINER_LIB, hdrs)):
+        return TRAINER_LIB
+    cmd = ["g++", "-std=c++20", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I/usr/local/cuda/include", TRAINER_SRC, "-o", TRAINER_LIB,
+           "-L" + HERE, "-lgradc_b200", "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed for trainer.cpp:\n" + r.stderr[-6000:])
+    if verbose:
+        print("linked", TRAINER_LIB)
+    return TRAINER_LIB
 
 
 if __name__ == "__main__":

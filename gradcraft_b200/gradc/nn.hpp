@@ -1,0 +1,850 @@
+// Module / Parameter / layers / GPT / AdamW / schedulers / clipper / data loader / checkpoints.
+//
+// API of the reference's gradc/nn tree (nn/base/module.hpp:8-126, parameter.hpp:9-67, initializers.hpp, layers/*.hpp,
+// optim/adam.hpp:12-246, sched/*.hpp, utils/*.hpp) as train.cpp uses it.  Differences underneath:
+//   * Module::to(Device) packs every parameter into one ParamArena (weights, gradients and later the AdamW moments are
+//     parallel contiguous arrays), ordered by the order in which gradients become final in backward, cut into buckets;
+//   * AdamW::step is one fused launch over that arena (bias corrections on the host, hyper-parameters by value, the
+//     clip factor folded in) instead of one launch per tensor reading seven device scalars;
+//   * GlobalNormClipper::normalize is one sum-of-squares over the gradient arena and one scalar read-back.
+#pragma once
+
+#include <cmath>
+#include <filesystem>
+#include <fstream>
+#include <numbers>
+#include <random>
+#include <string>
+#include <unordered_map>
+
+#include "ops.hpp"
+
+namespace gradc {
+
+// ---- parameters ------------------------------------------------------------------------------------------------------
+template <typename T>
+requires std::is_floating_point_v<T>
+class Parameter {
+    Tensor<T> m_tensor;
+    bool m_no_decay = false;
+    void validate() const {
+        if (!m_tensor.is_dense()) throw std::runtime_error("Parameters must be dense tensors (contiguous, volume == storage size).");
+    }
+
+public:
+    Parameter() = default;
+    Parameter(const Tensor<T>& t) : m_tensor(t) { validate(); m_tensor.set_requires_grad(true); }
+    Parameter(Tensor<T>&& t) : m_tensor(std::move(t)) { validate(); m_tensor.set_requires_grad(true); }
+    Parameter(Parameter&&) noexcept = default;
+    Parameter& operator=(Parameter&&) noexcept = default;
+    Parameter(const Parameter&) = delete;
+    Parameter& operator=(const Parameter&) = delete;
+    operator Tensor<T>() const { return m_tensor; }
+    Tensor<T>& tensor() { return m_tensor; }
+    const Tensor<T>& tensor() const { return m_tensor; }
+    std::optional<Tensor<T>> grad() const { return m_tensor.grad(); }
+    Device device() const { return m_tensor.device(); }
+    void zero_grad() { m_tensor.zero_grad(); }
+    bool requires_grad() const { return m_tensor.requires_grad(); }
+    void set_requires_grad(bool v) { m_tensor.set_requires_grad(v); }
+    bool no_decay() const { return m_no_decay; }
+    void set_no_decay(bool v) { m_no_decay = v; }
+};
+
+// ---- initializers ----------------------------------------------------------------------------------------------------
+template <typename T>
+class Initializer {
+public:
+    virtual ~Initializer() = default;
+    virtual Tensor<T> generate(const std::vector<int64_t>& shape, Device device) const = 0;
+};
+template <typename T>
+class ZerosInit : public Initializer<T> {
+public:
+    Tensor<T> generate(const std::vector<int64_t>& shape, Device device) const override { return Tensor<T>::zeros(shape, device); }
+};
+template <typename T>
+class OnesInit : public Initializer<T> {
+public:
+    Tensor<T> generate(const std::vector<int64_t>& shape, Device device) const override { return Tensor<T>::ones(shape, device); }
+};
+template <typename T>
+class NormalInit : public Initializer<T> {
+    T m_mean, m_std;
+
+public:
+    NormalInit(T mean, T std) : m_mean(mean), m_std(std) {}
+    Tensor<T> generate(const std::vector<int64_t>& shape, Device device) const override { return Tensor<T>::normal(shape, m_mean, m_std, device); }
+};
+
+// ---- module ------------------------------------------------------------------------------------------------------------
+template <typename T>
+class Module {
+protected:
+    bool m_is_training = true;
+    std::vector<std::pair<std::string, Module<T>*>> m_submodules;
+    std::vector<std::pair<std::string, Parameter<T>*>> m_parameters;
+
+    static int64_t bucket_elems() {
+        int64_t mb = 25;
+        if (const char* e = std::getenv("GRADC_BUCKET_MB")) mb = std::max<int64_t>(1, std::atoll(e));
+        return mb * 1024 * 1024 / (int64_t)sizeof(float);
+    }
+
+public:
+    virtual ~Module() = default;
+    bool is_training() const { return m_is_training; }
+    void train() { m_is_training = true; for (auto& [n, m] : m_submodules) m->train(); }
+    void eval() { m_is_training = false; for (auto& [n, m] : m_submodules) m->eval(); }
+    void register_module(std::string prefix, Module<T>* module) { m_submodules.emplace_back(std::move(prefix), module); }
+    void register_parameter(std::string prefix, Parameter<T>* param) { m_parameters.emplace_back(std::move(prefix), param); }
+
+    // registration order: own parameters, then submodules depth first (the order forward() touches them)
+    void ordered_parameters(std::vector<std::pair<std::string, Parameter<T>*>>& out, const std::string& prefix = "") const {
+        for (const auto& [n, p] : m_parameters) out.emplace_back(prefix.empty() ? n : prefix + "." + n, p);
+        for (const auto& [n, m] : m_submodules) m->ordered_parameters(out, prefix.empty() ? n : prefix + "." + n);
+    }
+    std::unordered_map<std::string, Parameter<T>*> named_parameters(std::string prefix = "") const {
+        std::vector<std::pair<std::string, Parameter<T>*>> v;
+        ordered_parameters(v, prefix);
+        return std::unordered_map<std::string, Parameter<T>*>(v.begin(), v.end());
+    }
+    std::vector<Parameter<T>*> parameters() {
+        std::vector<std::pair<std::string, Parameter<T>*>> v;
+        ordered_parameters(v);
+        std::vector<Parameter<T>*> r;
+        for (auto& kv : v) r.push_back(kv.second);
+        return r;
+    }
+    std::unordered_map<std::string, Tensor<T>> state_dict(Device device = Device(DeviceType::CPU)) const {
+        std::unordered_map<std::string, Tensor<T>> d;
+        for (const auto& [name, p] : named_parameters()) {
+            Tensor<T> moved = p->tensor().to(device);
+            moved.realize();
+            d[name] = moved.detach();
+        }
+        return d;
+    }
+    void load_state_dict(const std::unordered_map<std::string, Tensor<T>>& sd) {
+        for (const auto& [name, p] : named_parameters()) {
+            auto it = sd.find(name);
+            if (it == sd.end()) {
+                std::cout << "Warning: '" + name + "' is in the model, but couldn't find its counterpart in state_dict during loading." << std::endl;
+                continue;
+            }
+            if (it->second.volume() != p->tensor().volume()) throw std::runtime_error("load_state_dict: size mismatch for " + name);
+            Tensor<T> src = it->second;
+            src.realize();
+            if (p->tensor()._get_state()->m_slot.arena) {  // arena-resident: overwrite the slice, keep the slot
+                if (src.device().is_cuda()) {
+                    Tensor<T> dst = p->tensor();
+                    copy_or_add(dst, make_contiguous(src), false);
+                } else {
+                    gcb_check(gcb_copy_h2d(Backend::get().ctx(p->device()), p->tensor().data_ptr(), src.data_ptr(), sizeof(T) * (size_t)src.volume()), "load_state_dict");
+                }
+            } else {
+                Tensor<T> moved = src.to(p->tensor().device());
+                moved.realize();
+                Tensor<T> leaf = Tensor<T>(p->tensor().shape(), dense_strides(p->tensor().shape()), moved.offset(), moved._get_storage(), false);
+                leaf.set_requires_grad(p->requires_grad());
+                p->tensor() = std::move(leaf);
+            }
+        }
+    }
+    void zero_grad() {
+        std::shared_ptr<ParamArena> arena;
+        for (Parameter<T>* p : parameters()) {
+            p->zero_grad();
+            if (p->tensor()._get_state()->m_slot.arena) arena = p->tensor()._get_state()->m_slot.arena;
+        }
+        if (arena) arena->on_zero_grad();
+    }
+
+    // Eager move.  On a CUDA device every parameter becomes a slice of one arena, in reverse registration order:
+    // the head / last block first and the token embedding last — the order in which backward finishes their gradients.
+    void to(Device device) {
+        std::vector<std::pair<std::string, Parameter<T>*>> ordered;
+        ordered_parameters(ordered);
+        if (device.is_cpu()) {
+            for (auto& [name, p] : ordered) {
+                Tensor<T> moved = p->tensor().to(device);
+                moved.realize();
+                Tensor<T> leaf = moved.detach();
+                leaf.set_requires_grad(p->requires_grad());
+                p->tensor() = std::move(leaf);
+            }
+            return;
+        }
+        if constexpr (std::is_same_v<T, float>) {
+            std::reverse(ordered.begin(), ordered.end());
+            auto arena = std::make_shared<ParamArena>();
+            arena->device = device;
+            const int64_t bucket_cap = bucket_elems();
+            int64_t off = 0, bucket_begin = 0;
+            for (auto& [name, p] : ordered) {
+                ParamArena::Slot s;
+                s.name = name;
+                s.size = p->tensor().volume();
+                s.padded = (s.size + GCB_ADAMW_CHUNK - 1) / GCB_ADAMW_CHUNK * GCB_ADAMW_CHUNK;
+                s.offset = off;
+                s.no_decay = p->no_decay();
+                s.bucket = (int)arena->buckets.size();
+                off += s.padded;
+                arena->slots.push_back(s);
+                if (off - bucket_begin >= bucket_cap) {
+                    arena->buckets.push_back({bucket_begin, off, 0, 0, false});
+                    bucket_begin = off;
+                }
+            }
+            if (off > bucket_begin || arena->buckets.empty()) arena->buckets.push_back({bucket_begin, off, 0, 0, false});
+            for (auto& s : arena->slots) arena->buckets[s.bucket].n_slots++;
+            arena->total = off;
+            Backend& be = Backend::get();
+            gcb_ctx* c = be.ctx(device);
+            arena->w = static_cast<float*>(be.allocate(off * (int64_t)sizeof(float), device));
+            arena->g = static_cast<float*>(be.allocate(off * (int64_t)sizeof(float), device));
+            gcb_check(gcb_fill_f32(c, arena->w, 0.0f, off), "arena clear");
+            gcb_check(gcb_fill_f32(c, arena->g, 0.0f, off), "arena clear");
+            for (size_t i = 0; i < ordered.size(); ++i) {
+                Parameter<T>* p = ordered[i].second;
+                ParamArena::Slot& s = arena->slots[i];
+                Tensor<T> src = p->tensor();
+                src.realize();
+                if (src.device().is_cpu()) gcb_check(gcb_copy_h2d(c, arena->w + s.offset, src.data_ptr(), sizeof(float) * (size_t)s.size), "parameter upload");
+                else gcb_check(gcb_copy_d2d(c, arena->w + s.offset, src.data_ptr(), sizeof(float) * (size_t)s.size), "parameter move");
+                auto storage = std::make_shared<Storage<float>>(arena->w + s.offset, s.size, device, std::shared_ptr<void>(arena, (void*)arena->w));
+                Tensor<float> leaf(src.shape(), dense_strides(src.shape()), 0, std::move(storage), false);
+                leaf._get_state()->m_slot = {arena, (int)i};
+                leaf._get_state()->m_is_realized = true;
+                leaf.set_requires_grad(p->requires_grad());
+                p->tensor() = std::move(leaf);
+            }
+            gcb_check(gcb_ctx_sync(c), "parameter upload");
+            if (const char* e = std::getenv("GRADC_ACCUM_STEPS")) arena->accum_expected = std::atoll(e);
+        } else {
+            throw std::runtime_error("Module::to(CUDA): float modules only");
+        }
+    }
+    int64_t num_params() {
+        int64_t n = 0;
+        for (Parameter<T>* p : parameters()) n += p->tensor()._get_storage()->size();
+        return n;
+    }
+    // The arena the parameters live in after to(CUDA) (null before).
+    std::shared_ptr<ParamArena> arena() {
+        auto ps = parameters();
+        return ps.empty() ? nullptr : ps[0]->tensor()._get_state()->m_slot.arena;
+    }
+};
+
+// ---- layers ------------------------------------------------------------------------------------------------------------
+template <typename T>
+requires std::is_floating_point_v<T>
+class Linear : public Module<T> {
+    Parameter<T> m_weight, m_bias;
+
+public:
+    Linear(int64_t in, int64_t out, const Initializer<T>& w_init, const Initializer<T>& b_init) {
+        m_weight = Parameter<T>(w_init.generate({in, out}, Device(DeviceType::CPU)));
+        m_bias = Parameter<T>(b_init.generate({out}, Device(DeviceType::CPU)));
+        m_bias.set_no_decay(true);
+        this->register_parameter("W", &m_weight);
+        this->register_parameter("b", &m_bias);
+    }
+    // matmul + bias in one GEMM whose epilogue adds the bias row
+    Tensor<T> forward(Tensor<T> x) { return linear(std::move(x), m_weight.tensor(), m_bias.tensor()); }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class MultiHeadAttention : public Module<T> {
+    Linear<T> m_q_proj, m_k_proj, m_v_proj, m_out_proj;
+    int64_t m_num_heads, m_head_dim;
+    bool m_is_causal;
+
+public:
+    MultiHeadAttention(int64_t embed_dim, int64_t num_heads, bool is_causal, int64_t /*max_seq_len*/, const Initializer<T>& proj_w_init, const Initializer<T>& residual_w_init, const Initializer<T>& proj_b_init)
+        : m_q_proj(embed_dim, embed_dim, proj_w_init, proj_b_init), m_k_proj(embed_dim, embed_dim, proj_w_init, proj_b_init), m_v_proj(embed_dim, embed_dim, proj_w_init, proj_b_init),
+          m_out_proj(embed_dim, embed_dim, residual_w_init, proj_b_init), m_is_causal(is_causal) {
+        if (embed_dim % num_heads != 0) throw std::runtime_error("embed_dim modulo num_heads must = 0 in MHA.");
+        m_num_heads = num_heads;
+        m_head_dim = embed_dim / num_heads;
+        this->register_module("q_proj", &m_q_proj);
+        this->register_module("k_proj", &m_k_proj);
+        this->register_module("v_proj", &m_v_proj);
+        this->register_module("out_proj", &m_out_proj);
+    }
+    Tensor<T> forward(Tensor<T> x) {  // (B, T, C)
+        const int64_t B = x.shape()[0], S = x.shape()[1];
+        auto heads = [&](Tensor<T> t) { return t.reshape({B, S, m_num_heads, m_head_dim}).permute({0, 2, 1, 3}); };  // views only
+        Tensor<T> Q = heads(m_q_proj.forward(x)), K = heads(m_k_proj.forward(x)), V = heads(m_v_proj.forward(x));
+        Tensor<T> attn = sdpa(Q, K, V, m_is_causal);
+        attn = attn.permute({0, 2, 1, 3}).reshape({B, S, m_num_heads * m_head_dim});  // a view: sdpa lays its output out (B, T, H, D)
+        return m_out_proj.forward(attn);
+    }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class LayerNorm : public Module<T> {
+    Parameter<T> m_gamma, m_beta;
+    std::vector<int64_t> m_axes;
+    T m_eps;
+
+public:
+    LayerNorm(const std::vector<int64_t>& param_shape, const std::vector<int64_t>& axes, const Initializer<T>& gamma_init, const Initializer<T>& beta_init, T eps = static_cast<T>(1e-5))
+        : m_axes(axes), m_eps(eps) {
+        m_gamma = Parameter<T>(gamma_init.generate(param_shape, Device(DeviceType::CPU)));
+        m_beta = Parameter<T>(beta_init.generate(param_shape, Device(DeviceType::CPU)));
+        m_gamma.set_no_decay(true);
+        m_beta.set_no_decay(true);
+        this->register_parameter("gamma", &m_gamma);
+        this->register_parameter("beta", &m_beta);
+    }
+    Tensor<T> forward(Tensor<T> x) { return layernorm(std::move(x), m_gamma.tensor(), m_beta.tensor(), m_axes, m_eps); }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class RMSNorm : public Module<T> {
+    Parameter<T> m_gamma;
+    std::vector<int64_t> m_axes;
+    T m_eps;
+
+public:
+    RMSNorm(const std::vector<int64_t>& param_shape, const std::vector<int64_t>& axes, const Initializer<T>& gamma_init, T eps = static_cast<T>(1e-6)) : m_axes(axes), m_eps(eps) {
+        m_gamma = Parameter<T>(gamma_init.generate(param_shape, Device(DeviceType::CPU)));
+        m_gamma.set_no_decay(true);
+        this->register_parameter("gamma", &m_gamma);
+    }
+    Tensor<T> forward(Tensor<T> x) { return rmsnorm(std::move(x), m_gamma.tensor(), m_axes, m_eps, true); }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class Embedding : public Module<T> {
+    Parameter<T> m_embeds;
+
+public:
+    Embedding(int64_t rows, std::vector<int64_t> embed_dim, const Initializer<T>& init) {
+        embed_dim.insert(embed_dim.begin(), rows);
+        m_embeds = Parameter<T>(init.generate(embed_dim, Device(DeviceType::CPU)));
+        m_embeds.set_no_decay(true);
+        this->register_parameter("embeds", &m_embeds);
+    }
+    Tensor<T> forward(Tensor<int64_t> indices) { return embed(std::move(indices), m_embeds.tensor()); }
+    const Tensor<T>& weight() const { return m_embeds.tensor(); }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class PosEncoding : public Module<T> {
+    Parameter<T> m_pos_embeds;
+    Tensor<int64_t> m_token_range;
+
+public:
+    PosEncoding(int64_t max_seq_len, std::vector<int64_t> dim, const Initializer<T>& init) {
+        dim.insert(dim.begin(), max_seq_len);
+        m_pos_embeds = Parameter<T>(init.generate(dim, Device(DeviceType::CPU)));
+        m_pos_embeds.set_no_decay(true);
+        m_token_range = Tensor<int64_t>::arange(0, max_seq_len, 1);
+        this->register_parameter("pos_embeds", &m_pos_embeds);
+    }
+    Tensor<T> forward(int64_t seq_len) {
+        if (m_token_range.device() != m_pos_embeds.device()) m_token_range = Tensor<int64_t>::arange(0, m_token_range.volume(), 1, m_pos_embeds.device());
+        return embed(m_token_range[Slice(0, seq_len)], m_pos_embeds.tensor());
+    }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class SwiGLUMLP : public Module<T> {
+    Linear<T> m_w1, m_w2, m_w3;
+
+public:
+    SwiGLUMLP(int64_t embed_dim, int64_t hidden_dim, const Initializer<T>& base_init, const Initializer<T>& residual_init)
+        : m_w1(embed_dim, hidden_dim, base_init, ZerosInit<T>()), m_w2(embed_dim, hidden_dim, base_init, ZerosInit<T>()), m_w3(hidden_dim, embed_dim, residual_init, ZerosInit<T>()) {
+        this->register_module("w1", &m_w1);
+        this->register_module("w2", &m_w2);
+        this->register_module("w3", &m_w3);
+    }
+    Tensor<T> forward(Tensor<T> x) { return m_w3.forward(swiglu_fast(m_w1.forward(x), m_w2.forward(x))); }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class GeluMLP : public Module<T> {
+    Linear<T> m_fc1, m_fc2;
+
+public:
+    GeluMLP(int64_t embed_dim, int64_t hidden_dim, const Initializer<T>& base_init, const Initializer<T>& residual_init)
+        : m_fc1(embed_dim, hidden_dim, base_init, ZerosInit<T>()), m_fc2(hidden_dim, embed_dim, residual_init, ZerosInit<T>()) {
+        this->register_module("fc1", &m_fc1);
+        this->register_module("fc2", &m_fc2);
+    }
+    Tensor<T> forward(Tensor<T> x) { return m_fc2.forward(m_fc1.forward(x).gelu()); }
+};
+
+// pre-norm residual block; Norm / MLP pick the architecture (RMSNorm + SwiGLU as gradc::GPT, or LayerNorm + GELU)
+template <typename T, class Norm, class MLP>
+class BlockT : public Module<T> {
+    Norm m_norm1;
+    MultiHeadAttention<T> m_attn;
+    Norm m_norm2;
+    MLP m_mlp;
+
+public:
+    template <class NormMaker>
+    BlockT(int64_t C, int64_t H, int64_t max_seq, int64_t hidden, const Initializer<T>& base_init, const Initializer<T>& residual_init, NormMaker mk)
+        : m_norm1(mk()), m_attn(C, H, true, max_seq, base_init, residual_init, ZerosInit<T>()), m_norm2(mk()), m_mlp(C, hidden, base_init, residual_init) {
+        this->register_module("norm1", &m_norm1);
+        this->register_module("attn", &m_attn);
+        this->register_module("norm2", &m_norm2);
+        this->register_module("mlp", &m_mlp);
+    }
+    Tensor<T> forward(Tensor<T> x) {
+        x = x + m_attn.forward(m_norm1.forward(x));
+        x = x + m_mlp.forward(m_norm2.forward(x));
+        return x;
+    }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class TransformerBlock : public BlockT<T, RMSNorm<T>, SwiGLUMLP<T>> {
+public:
+    TransformerBlock(int64_t C, int64_t H, int64_t max_seq, const Initializer<T>& base_init, const Initializer<T>& residual_init, T eps = static_cast<T>(1e-5))
+        : BlockT<T, RMSNorm<T>, SwiGLUMLP<T>>(C, H, max_seq, 3 * C, base_init, residual_init, [&] { return RMSNorm<T>({C}, {-1}, OnesInit<T>(), eps); }) {}
+};
+
+template <typename T, class Norm, class Block>
+class GPTBase : public Module<T> {
+protected:
+    Embedding<T> m_token_embed;
+    PosEncoding<T> m_pos_embed;
+    std::vector<std::unique_ptr<Block>> m_blocks;
+    Norm m_final_norm;
+
+    template <class NormMaker>
+    GPTBase(int64_t V, int64_t max_seq, int64_t C, const Initializer<T>& base_init, NormMaker mk)
+        : m_token_embed(V, {C}, NormalInit<T>(0, static_cast<T>(0.02))), m_pos_embed(max_seq, {C}, base_init), m_final_norm(mk()) {
+        this->register_module("token_embed", &m_token_embed);
+        this->register_module("pos_embed", &m_pos_embed);
+    }
+    void finish_registration() { this->register_module("final_norm", &m_final_norm); }
+
+public:
+    Tensor<T> forward(Tensor<int64_t> indices) {  // (B, T) -> logits (B, T, V)
+        const int64_t S = indices.shape()[1];
+        Tensor<T> x = m_token_embed.forward(indices) + m_pos_embed.forward(S);
+        for (auto& b : m_blocks) x = b->forward(x);
+        x = m_final_norm.forward(x);
+        return matmul(x, m_token_embed.weight().transpose(0, 1));  // tied head
+    }
+};
+
+// gradc::GPT as shipped: RMSNorm + SwiGLU(3C) + learned positions + tied head (nn/layers/gpt.hpp:70-112)
+template <typename T>
+requires std::is_floating_point_v<T>
+class GPT : public GPTBase<T, RMSNorm<T>, TransformerBlock<T>> {
+public:
+    GPT(int64_t V, int64_t max_seq, int64_t C, int64_t H, int64_t L, const Initializer<T>& base_init, const Initializer<T>& residual_init, T eps = static_cast<T>(1e-5))
+        : GPTBase<T, RMSNorm<T>, TransformerBlock<T>>(V, max_seq, C, base_init, [&] { return RMSNorm<T>({C}, {-1}, OnesInit<T>(), eps); }) {
+        for (int64_t i = 0; i < L; ++i) {
+            this->m_blocks.push_back(std::make_unique<TransformerBlock<T>>(C, H, max_seq, base_init, residual_init, eps));
+            this->register_module("block_" + std::to_string(i), this->m_blocks.back().get());
+        }
+        this->finish_registration();
+    }
+    GPT(const GPTConfig& cfg, const Initializer<T>& base_init, const Initializer<T>& residual_init)
+        : GPT(cfg.vocab_size, cfg.max_seq_len, cfg.embed_dim, cfg.num_heads, cfg.num_layers, base_init, residual_init, cfg.calc_eps) {}
+};
+
+// The LayerNorm + GELU(d_ff) transformer assembled from the reference's primitives layernorm() and Tensor::gelu().
+template <typename T>
+requires std::is_floating_point_v<T>
+class LayerNormGPT : public GPTBase<T, LayerNorm<T>, BlockT<T, LayerNorm<T>, GeluMLP<T>>> {
+    using Block = BlockT<T, LayerNorm<T>, GeluMLP<T>>;
+
+public:
+    LayerNormGPT(int64_t V, int64_t max_seq, int64_t C, int64_t H, int64_t L, int64_t d_ff, const Initializer<T>& base_init, const Initializer<T>& residual_init, T eps = static_cast<T>(1e-5))
+        : GPTBase<T, LayerNorm<T>, Block>(V, max_seq, C, base_init, [&] { return LayerNorm<T>({C}, {-1}, OnesInit<T>(), ZerosInit<T>(), eps); }) {
+        for (int64_t i = 0; i < L; ++i) {
+            this->m_blocks.push_back(std::make_unique<Block>(C, H, max_seq, d_ff, base_init, residual_init, [&] { return LayerNorm<T>({C}, {-1}, OnesInit<T>(), ZerosInit<T>(), eps); }));
+            this->register_module("block_" + std::to_string(i), this->m_blocks.back().get());
+        }
+        this->finish_registration();
+    }
+};
+
+// ---- optimizer ---------------------------------------------------------------------------------------------------------
+template <typename T>
+requires std::is_floating_point_v<T>
+class Optimizer {
+protected:
+    std::unordered_map<std::string, Parameter<T>*> m_named_params;
+    T m_lr = T(0);
+
+public:
+    virtual ~Optimizer() = default;
+    Device optim_device() { return m_named_params.begin()->second->device(); }
+    void assert_valid_params() {
+        if (m_named_params.empty()) throw std::runtime_error("Passed a vector of 0 parameters into the optimizer.");
+        Device d = optim_device();
+        for (auto& [n, p] : m_named_params) if (p->device() != d) throw std::runtime_error("All parameters passed into the optimizer must be on the same device.");
+    }
+    virtual std::unordered_map<std::string, Tensor<T>> state_dict(Device) { return {}; }
+    virtual void load_state_dict(const std::unordered_map<std::string, Tensor<T>>&) {}
+    void update_lr(T lr) { m_lr = lr; }  // by value: no one-element device tensor, no <<<1,1>>> launch
+    T lr() const { return m_lr; }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class AdamW : public Optimizer<T> {
+    T m_beta1, m_beta2, m_weight_decay, m_eps;
+    T m_beta1_exp = T(1), m_beta2_exp = T(1);
+    std::shared_ptr<ParamArena> m_arena;  // set when the parameters are exactly one arena
+    std::unordered_map<std::string, Tensor<T>> m_first_moment, m_second_moment;
+
+    Tensor<T> moment_slice(float* base, const ParamArena::Slot& s, const std::vector<int64_t>& shape) {
+        auto st = std::make_shared<Storage<T>>(base + s.offset, s.size, m_arena->device, std::shared_ptr<void>(m_arena, (void*)base));
+        return Tensor<T>(shape, dense_strides(shape), 0, std::move(st), false);
+    }
+
+public:
+    AdamW(std::unordered_map<std::string, Parameter<T>*> named_params, T lr, T beta1 = static_cast<T>(0.9), T beta2 = static_cast<T>(0.999), T weight_decay = static_cast<T>(0.0), T eps = static_cast<T>(1e-8))
+        : m_beta1(beta1), m_beta2(beta2), m_weight_decay(weight_decay), m_eps(eps) {
+        this->m_named_params = std::move(named_params);
+        this->assert_valid_params();
+        this->m_lr = lr;
+        Device d = this->optim_device();
+        if (!d.is_cuda()) throw std::runtime_error("AdamW: parameters must live on a CUDA device (call model.to(gpu) first)");
+        // arena mode: every slot of one arena is covered by a parameter of this optimizer
+        std::shared_ptr<ParamArena> a = this->m_named_params.begin()->second->tensor()._get_state()->m_slot.arena;
+        bool whole = a != nullptr && a->slots.size() == this->m_named_params.size();
+        if (whole) for (auto& [n, p] : this->m_named_params) whole = whole && p->tensor()._get_state()->m_slot.arena == a;
+        if (whole) {
+            m_arena = a;
+            Backend& be = Backend::get();
+            gcb_ctx* c = be.ctx(d);
+            const int64_t bytes = a->total * (int64_t)sizeof(float);
+            if (!a->m) { a->m = static_cast<float*>(be.allocate(bytes, d)); a->v = static_cast<float*>(be.allocate(bytes, d)); }
+            gcb_check(gcb_fill_f32(c, a->m, 0.0f, a->total), "moment clear");
+            gcb_check(gcb_fill_f32(c, a->v, 0.0f, a->total), "moment clear");
+            const int64_t chunks = a->total / GCB_ADAMW_CHUNK;
+            std::vector<uint8_t> mask((size_t)chunks, 0);
+            for (auto& s : a->slots)
+                if (!s.no_decay) std::fill(mask.begin() + s.offset / GCB_ADAMW_CHUNK, mask.begin() + (s.offset + s.padded) / GCB_ADAMW_CHUNK, uint8_t(1));
+            if (!a->decay_mask) a->decay_mask = static_cast<uint8_t*>(be.allocate(chunks, d));
+            gcb_check(gcb_copy_h2d(c, a->decay_mask, mask.data(), (size_t)chunks), "decay mask upload");
+            for (auto& [n, p] : this->m_named_params) {
+                const ParamArena::Slot& s = a->slots[p->tensor()._get_state()->m_slot.slot];
+                m_first_moment[n] = moment_slice(a->m, s, p->tensor().shape());
+                m_second_moment[n] = moment_slice(a->v, s, p->tensor().shape());
+            }
+        } else {
+            for (auto& [n, p] : this->m_named_params) {
+                m_first_moment[n] = Tensor<T>(p->tensor().shape(), T(0), d);
+                m_second_moment[n] = Tensor<T>(p->tensor().shape(), T(0), d);
+            }
+        }
+    }
+
+    void step() {
+        Device d = this->optim_device();
+        gcb_ctx* c = Backend::get().ctx(d);
+        m_beta1_exp *= m_beta1;  // advanced before the update, as the reference does (adam.hpp:44-45)
+        m_beta2_exp *= m_beta2;
+        if (m_arena) {
+            m_arena->sync_gradients();
+            if (m_arena->all_grads_live()) {
+                gcb_check(gcb_adamw_arena_f32(c, m_arena->w, m_arena->m, m_arena->v, m_arena->g, m_arena->decay_mask, m_arena->total, this->m_lr, m_beta1, m_beta2, m_beta1_exp, m_beta2_exp,
+                                              m_weight_decay, m_eps, m_arena->pending_grad_scale), "AdamW step");
+                m_arena->pending_grad_scale = 1.0f;
+                return;
+            }
+        }
+        for (auto& [name, p] : this->m_named_params) {  // parameters without a gradient are skipped (adam.hpp:49-51)
+            std::optional<Tensor<T>> g = p->grad();
+            if (!g.has_value()) continue;
+            Tensor<T> gc = make_contiguous(g.value());
+            gcb_check(gcb_adamw_step_f32(c, p->tensor().data_ptr(), m_first_moment[name].data_ptr(), m_second_moment[name].data_ptr(), gc.data_ptr(), gc.volume(), this->m_lr, m_beta1, m_beta2,
+                                         m_beta1_exp, m_beta2_exp, m_weight_decay, m_eps, p->no_decay() ? 1 : 0, 1.0f), "AdamW step");
+        }
+    }
+
+    std::unordered_map<std::string, Tensor<T>> state_dict(Device device = Device(DeviceType::CPU)) override {
+        std::unordered_map<std::string, Tensor<T>> r;
+        auto put = [&](const std::string& key, const Tensor<T>& t) {
+            Tensor<T> moved = t.to(device);
+            moved.realize();
+            r[key] = moved.detach();
+        };
+        for (auto& [n, t] : m_first_moment) put(n + ".adamw_first", t);
+        for (auto& [n, t] : m_second_moment) put(n + ".adamw_second", t);
+        put("beta1_exp", Tensor<T>(m_beta1_exp, Device(DeviceType::CPU)));
+        put("beta2_exp", Tensor<T>(m_beta2_exp, Device(DeviceType::CPU)));
+        return r;
+    }
+    void load_state_dict(const std::unordered_map<std::string, Tensor<T>>& sd) override {
+        gcb_ctx* c = Backend::get().ctx(this->optim_device());
+        auto load = [&](std::unordered_map<std::string, Tensor<T>>& dst, const char* suffix) {
+            for (auto& [n, t] : dst) {
+                auto it = sd.find(n + suffix);
+                if (it == sd.end()) { std::cout << "Warning: '" + n + "' has no '" + suffix + "' entry in the optimizer state_dict." << std::endl; continue; }
+                Tensor<T> src = it->second;
+                src.realize();
+                if (src.device().is_cpu()) gcb_check(gcb_copy_h2d(c, t.data_ptr(), src.data_ptr(), sizeof(T) * (size_t)t.volume()), "optimizer state upload");
+                else { Tensor<T> d2 = t; copy_or_add(d2, make_contiguous(src), false); }
+            }
+        };
+        load(m_first_moment, ".adamw_first");
+        load(m_second_moment, ".adamw_second");
+        auto b1 = sd.find("beta1_exp"), b2 = sd.find("beta2_exp");
+        if (b1 == sd.end()) throw std::runtime_error("Tried loading AdamW optimizer with state_dict without key 'beta1_exp'");
+        if (b2 == sd.end()) throw std::runtime_error("Tried loading AdamW optimizer with state_dict without key 'beta2_exp'");
+        m_beta1_exp = b1->second.item();
+        m_beta2_exp = b2->second.item();
+    }
+    T beta1_exp() const { return m_beta1_exp; }
+    T beta2_exp() const { return m_beta2_exp; }
+};
+
+// ---- schedulers ------------------------------------------------------------------------------------------------------
+template <typename T>
+requires std::is_floating_point_v<T>
+class Scheduler {
+protected:
+    Optimizer<T>* m_optimizer;
+
+public:
+    int64_t m_t;
+    T m_lr;
+    Scheduler(Optimizer<T>* optimizer, T init_lr) : m_optimizer(optimizer), m_t(0), m_lr(init_lr) {}
+    virtual ~Scheduler() = default;
+    virtual void step() = 0;
+    virtual std::unordered_map<std::string, T> state_dict() const { return {{"m_t", static_cast<T>(m_t)}, {"m_lr", m_lr}}; }
+    virtual void load_state_dict(const std::unordered_map<std::string, T>& s) {
+        m_t = static_cast<int64_t>(s.at("m_t"));
+        m_lr = s.at("m_lr");
+        m_optimizer->update_lr(m_lr);
+    }
+};
+
+template <typename T>
+requires std::is_floating_point_v<T>
+class CosineScheduler : public Scheduler<T> {
+    T m_max_lr, m_min_lr;
+    int64_t m_warmup_steps, m_max_steps;
+
+public:
+    CosineScheduler(Optimizer<T>* opt, T max_lr, T min_lr, int64_t warmup_steps, int64_t max_steps)
+        : Scheduler<T>(opt, T(0)), m_max_lr(max_lr), m_min_lr(min_lr), m_warmup_steps(warmup_steps), m_max_steps(max_steps) {}
+    void step() override {  // linear warm-up, cosine decay, t advanced before use (cosine_scheduler.hpp:20-37)
+        const int64_t t = ++this->m_t;
+        if (t <= m_warmup_steps) this->m_lr = m_max_lr * (static_cast<T>(t) / static_cast<T>(m_warmup_steps));
+        else if (t >= m_max_steps) this->m_lr = m_min_lr;
+        else {
+            const T ratio = static_cast<T>(t - m_warmup_steps) / static_cast<T>(m_max_steps - m_warmup_steps);
+            const T coeff = static_cast<T>(0.5) * (static_cast<T>(1.0) + std::cos(std::numbers::pi_v<T> * ratio));
+            this->m_lr = m_min_lr + coeff * (m_max_lr - m_min_lr);
+        }
+        this->m_optimizer->update_lr(this->m_lr);
+    }
+    std::unordered_map<std::string, T> state_dict() const override {
+        auto s = Scheduler<T>::state_dict();
+        s["max_lr"] = m_max_lr; s["min_lr"] = m_min_lr;
+        s["warmup_steps"] = static_cast<T>(m_warmup_steps); s["max_steps"] = static_cast<T>(m_max_steps);
+        return s;
+    }
+    void load_state_dict(const std::unordered_map<std::string, T>& s) override {
+        Scheduler<T>::load_state_dict(s);
+        m_max_lr = s.at("max_lr"); m_min_lr = s.at("min_lr");
+        m_warmup_steps = static_cast<int64_t>(s.at("warmup_steps")); m_max_steps = static_cast<int64_t>(s.at("max_steps"));
+    }
+};
+
+// ---- gradient clipping ---------------------------------------------------------------------------------------------------
+template <typename T>
+class GlobalNormClipper {
+    T m_max_norm;
+
+public:
+    GlobalNormClipper(T max_norm = static_cast<T>(1.0)) : m_max_norm(max_norm) {}
+    // n = sqrt(sum g^2); if n > max: g *= max / (n + 1e-6)   (norm_clip.hpp:42-55).  With arena-resident parameters the
+    // scale is not applied here: it is handed to the optimizer step, which multiplies it in while it reads the gradients.
+    T normalize(const std::vector<Parameter<T>*>& params) {
+        if (params.empty()) return T(0);
+        Device d = params[0]->device();
+        gcb_ctx* c = Backend::get().ctx(d);
+        std::shared_ptr<ParamArena> a = params[0]->tensor()._get_state()->m_slot.arena;
+        bool whole = a != nullptr && a->slots.size() == params.size();
+        if (whole) for (auto* p : params) whole = whole && p->tensor()._get_state()->m_slot.arena == a;
+        Tensor<T> sq(std::vector<int64_t>{}, d, uninitialized);
+        if (whole && a->all_grads_live()) {
+            a->sync_gradients();
+            gcb_check(gcb_sum_squares_f32(c, sq.data_ptr(), a->g, a->total, 0), "gradient norm");
+            const T norm = std::sqrt(sq.item()) * std::abs(a->pending_grad_scale);
+            if (norm > m_max_norm) a->pending_grad_scale *= m_max_norm / (norm + static_cast<T>(1e-6));
+            return norm;
+        }
+        if (a) a->sync_gradients();
+        bool first = true;
+        for (auto* p : params) {
+            auto g = p->grad();
+            if (!g.has_value()) continue;
+            Tensor<T> gc = make_contiguous(g.value());
+            gcb_check(gcb_sum_squares_f32(c, sq.data_ptr(), gc.data_ptr(), gc.volume(), first ? 0 : 1), "gradient norm");
+            first = false;
+        }
+        if (first) return T(0);
+        const T norm = std::sqrt(sq.item());
+        if (norm > m_max_norm) {
+            const T s = m_max_norm / (norm + static_cast<T>(1e-6));
+            for (auto* p : params) {
+                auto g = p->grad();
+                if (!g.has_value()) continue;
+                if (!g.value().is_contiguous()) throw std::runtime_error("clip: gradients must be contiguous");
+                gcb_check(gcb_binary_scalar_f32(c, GCB_B_MUL, g.value().data_ptr(), g.value().data_ptr(), s, g.value().volume()), "gradient scale");
+            }
+        }
+        return norm;
+    }
+};
+
+// ---- data loader (host side; nn/utils/data_loader.hpp:13-92 of the reference) -----------------------------------------------
+class DataLoader {
+    std::ifstream m_in;
+    int64_t m_total_tokens = 0, m_seq_len = 0, m_total_sequences = 0, m_seq_cursor = 0;
+    std::vector<int64_t> m_sequence_indices;
+    std::mt19937_64 m_rng;
+    void shuffle_dataset() {
+        std::shuffle(m_sequence_indices.begin(), m_sequence_indices.end(), m_rng);
+        m_seq_cursor = 0;
+    }
+
+public:
+    DataLoader(const std::string& path, int64_t seq_len, uint64_t seed = 67) : m_seq_len(seq_len), m_rng(seed) {
+        m_in = std::ifstream(path, std::ios::binary);
+        if (!m_in) throw std::runtime_error("Unable to open dataset: " + path);
+        m_total_tokens = (int64_t)std::filesystem::file_size(path) / (int64_t)sizeof(uint32_t);
+        if (m_total_tokens <= m_seq_len + 1) throw std::runtime_error("Dataset too small for sequence length " + std::to_string(seq_len));
+        m_total_sequences = (m_total_tokens - 1) / m_seq_len;
+        m_sequence_indices.resize(m_total_sequences);
+        for (int64_t i = 0; i < m_total_sequences; ++i) m_sequence_indices[i] = i;
+        shuffle_dataset();
+    }
+    // windows of T+1 little-endian uint32 tokens; X = w[0:T], Y = w[1:T+1], widened to int64
+    std::pair<Tensor<int64_t>, Tensor<int64_t>> next_batch(int64_t B, int64_t T, Device cpu_device) {
+        if (T != m_seq_len) throw std::invalid_argument("Requested T does not match initialized seq_len.");
+        if (m_seq_cursor + B > m_total_sequences) shuffle_dataset();
+        Tensor<int64_t> X({B, T}, cpu_device, uninitialized), Y({B, T}, cpu_device, uninitialized);
+        int64_t *px = X.data_ptr(), *py = Y.data_ptr();
+        std::vector<uint32_t> raw((size_t)T + 1);
+        for (int64_t b = 0; b < B; ++b) {
+            const int64_t seq = m_sequence_indices[m_seq_cursor + b];
+            m_in.seekg(seq * T * (int64_t)sizeof(uint32_t));
+            m_in.read(reinterpret_cast<char*>(raw.data()), (T + 1) * (int64_t)sizeof(uint32_t));
+            for (int64_t t = 0; t < T; ++t) { px[b * T + t] = raw[t]; py[b * T + t] = raw[t + 1]; }
+        }
+        m_seq_cursor += B;
+        return {X, Y};
+    }
+    int64_t total_sequences() const { return m_total_sequences; }
+};
+
+// ---- checkpoints (nn/utils/checkpoint.hpp:12-145: byte-compatible files) ------------------------------------------------------
+template <typename T>
+void save_tensor_checkpoint(const std::unordered_map<std::string, Tensor<T>>& sd, const std::string& path) {
+    std::ofstream out(path, std::ios::binary);
+    if (!out) throw std::runtime_error("Failed to open file for saving: " + path);
+    auto w64 = [&](int64_t v) { out.write(reinterpret_cast<const char*>(&v), sizeof(v)); };
+    const uint32_t tag = sizeof(T);
+    out.write(reinterpret_cast<const char*>(&tag), sizeof(tag));
+    w64((int64_t)sd.size());
+    for (const auto& [name, t] : sd) {
+        if (!t.device().is_cpu() || !t.is_contiguous()) throw std::runtime_error("save_tensor_checkpoint: tensors must be contiguous host tensors (use state_dict(cpu))");
+        w64((int64_t)name.size());
+        out.write(name.data(), (std::streamsize)name.size());
+        w64((int64_t)t.shape().size());
+        out.write(reinterpret_cast<const char*>(t.shape().data()), (std::streamsize)(t.shape().size() * sizeof(int64_t)));
+        const int64_t bytes = t.volume() * (int64_t)sizeof(T);
+        w64(bytes);
+        out.write(reinterpret_cast<const char*>(t.data_ptr()), bytes);
+    }
+}
+template <typename T>
+std::unordered_map<std::string, Tensor<T>> load_tensor_checkpoint(const std::string& path) {
+    std::ifstream in(path, std::ios::binary);
+    if (!in) throw std::runtime_error("Failed to open file for loading: " + path);
+    auto r64 = [&]() { int64_t v = 0; in.read(reinterpret_cast<char*>(&v), sizeof(v)); return v; };
+    uint32_t tag = 0;
+    in.read(reinterpret_cast<char*>(&tag), sizeof(tag));
+    if (tag != sizeof(T)) throw std::runtime_error("Tried reading a file whose type is " + std::to_string(tag) + "-bytes with a type having " + std::to_string(sizeof(T)) + "-bytes.");
+    std::unordered_map<std::string, Tensor<T>> d;
+    const int64_t n = r64();
+    for (int64_t i = 0; i < n; ++i) {
+        std::string name((size_t)r64(), '\0');
+        in.read(name.data(), (std::streamsize)name.size());
+        std::vector<int64_t> shape((size_t)r64());
+        in.read(reinterpret_cast<char*>(shape.data()), (std::streamsize)(shape.size() * sizeof(int64_t)));
+        Tensor<T> t(shape, Device(DeviceType::CPU), uninitialized);
+        const int64_t bytes = r64();
+        if (bytes != t.volume() * (int64_t)sizeof(T)) throw std::runtime_error("checkpoint entry '" + name + "' has an inconsistent size");
+        in.read(reinterpret_cast<char*>(t.data_ptr()), bytes);
+        if (!in) throw std::runtime_error("checkpoint file is truncated: " + path);
+        d[name] = std::move(t);
+    }
+    return d;
+}
+template <typename T>
+void save_scalar_checkpoint(const std::unordered_map<std::string, T>& sd, const std::string& path) {
+    std::ofstream out(path, std::ios::binary);
+    if (!out) throw std::runtime_error("Failed to open file for saving: " + path);
+    const uint32_t tag = sizeof(T);
+    out.write(reinterpret_cast<const char*>(&tag), sizeof(tag));
+    const int64_t n = (int64_t)sd.size();
+    out.write(reinterpret_cast<const char*>(&n), sizeof(n));
+    for (const auto& [name, v] : sd) {
+        const int64_t len = (int64_t)name.size();
+        out.write(reinterpret_cast<const char*>(&len), sizeof(len));
+        out.write(name.data(), len);
+        out.write(reinterpret_cast<const char*>(&v), sizeof(T));
+    }
+}
+template <typename T>
+std::unordered_map<std::string, T> load_scalar_checkpoint(const std::string& path) {
+    std::ifstream in(path, std::ios::binary);
+    if (!in) throw std::runtime_error("Failed to open file for loading: " + path);
+    uint32_t tag = 0;
+    in.read(reinterpret_cast<char*>(&tag), sizeof(tag));
+    if (tag != sizeof(T)) throw std::runtime_error("Tried reading a file whose type is " + std::to_string(tag) + "-bytes with a type having " + std::to_string(sizeof(T)) + "-bytes.");
+    int64_t n = 0;
+    in.read(reinterpret_cast<char*>(&n), sizeof(n));
+    std::unordered_map<std::string, T> d;
+    for (int64_t i = 0; i < n; ++i) {
+        int64_t len = 0;
+        in.read(reinterpret_cast<char*>(&len), sizeof(len));
+        std::string name((size_t)len, '\0');
+        in.read(name.data(), len);
+        T v;
+        in.read(reinterpret_cast<char*>(&v), sizeof(T));
+        d[name] = v;
+    }
+    return d;
+}
+inline void save_gpt_config(const GPTConfig& cfg, const std::string& path) {
+    std::ofstream out(path, std::ios::binary);
+    if (!out) throw std::runtime_error("Failed to open file for saving config: " + path);
+    out.write(reinterpret_cast<const char*>(&cfg), sizeof(GPTConfig));
+}
+inline GPTConfig load_gpt_config(const std::string& path) {
+    std::ifstream in(path, std::ios::binary);
+    if (!in) throw std::runtime_error("Failed to open file for loading config: " + path);
+    GPTConfig cfg;
+    in.read(reinterpret_cast<char*>(&cfg), sizeof(GPTConfig));
+    return cfg;
+}
+
+}  // namespace gradc
