@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Benchmark driver: GPT fp32 training throughput (fwd + bwd + AdamW), tokens/s.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gpt180m|gpt90m|tiny|kernels]
+
+Default workload "gpt180m": 12 layers, d_model 1024, 16 heads, d_ff 4096, seq 1024, vocab 32768, 32 sequences per GPU
+(LayerNorm + GELU, learned positions, tied head), Zipf(1.1) synthetic tokens, seeded N(0, 0.02) weights.
+One "step" = zero_grad + forward + Tensor::backward() + AdamW over one batch.  For N > 1 the script runs under
+torch.distributed.run (one rank per GPU); gradients are averaged by bucketed NCCL all-reduce overlapped with backward.
+
+Prints one JSON line (rank 0):
+  value     whole-job tokens/s with the token batches already resident in HBM, CUDA-event timed on the compute stream;
+  e2e       the same through the public trainer call with pinned HOST token buffers, the H2D copies and a D2H read of
+            the loss inside the timed region;
+  roofline  the GEMM engine (dominant kernel): algorithmic FLOP/s over the launches of the timed region vs the measured
+            dense tensor peak;
+  cpu_baseline  the reference's own CPU path (oracle/_ref) timed on the host cores on a bounded sample.
+`--impl reference` times that CPU path alone on the same metric.
+`--workload kernels` reports the fused backward kernels of the microbenchmark configuration against the HBM roofline.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: arch, V, T, C, H, L, F, B per GPU, micro-batches per step
+    "gpt180m": ("lngelu", 32768, 1024, 1024, 16, 12, 4096, 32, 1),
+    "gpt90m": ("lngelu", 16384, 512, 768, 12, 12, 3072, 32, 16),
+    "tiny": ("lngelu", 512, 64, 128, 4, 2, 512, 4, 1),
+}
+HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, wd=0.1, eps=1e-5, norm_eps=1e-5, ce_eps=1e-5)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], tensor_tflops=d.get("bf16_tflops_sustained", d["bf16_tflops"]), tensor_tflops_burst=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, tensor_tflops=1400.0, tensor_tflops_burst=1590.0, source="fallback")
+
+
+def flops_per_token(V, T, C, L, F):
+    """6 * (L * (4 C^2 + 2 C F) + C V) + 12 L T C: dense fwd + bwd contractions, non-causal attention as the reference computes it."""
+    return 6 * (L * (4 * C * C + 2 * C * F) + C * V) + 12 * L * T * C
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        mhz, reasons, mx = [], set(), None
+        for r in self.rows:
+            try:
+                mhz.append(float(r[0]))
+                mx = float(r[1])
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                pass
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "samples": len(mhz), "reasons": sorted(reasons)}
+
+
+# ---- reference CPU arm -------------------------------------------------------------------------------------
+def reference_cpu_run(workload, steps, warmup, sample_B=1):
+    """Times oracle/_ref/ref_harness (GradCraft's CPUBackend + OpenBLAS) on `steps` steps of a bounded sample:
+    the workload's model and sequence length with sample_B sequences per step.  Returns (tokens/s, description)."""
+    arch, V, T, C, H, L, F, B, accum = WORKLOADS[workload]
+    harness = os.path.join(ROOT, "oracle", "_ref", "ref_harness")
+    cores = os.cpu_count() or 1
+    if not os.path.exists(harness):
+        return None, cores, "oracle/_ref/ref_harness is not built", "reference"
+    import numpy as np
+
+    from gradcraft_b200 import synth
+
+    n_steps = steps + warmup
+    with tempfile.TemporaryDirectory() as tmp:
+        synth.token_batches(99, n_steps, sample_B, T, V).tofile(os.path.join(tmp, "tok.i64"))
+        h = HYPER
+        cmd = [harness, "gpt", arch] + [str(v) for v in (V, T, C, H, L, F, sample_B, n_steps, 1, h["lr"], h["beta1"], h["beta2"], h["wd"], h["eps"], 0.0)]
+        cmd += ["-", os.path.join(tmp, "tok.i64"), os.path.join(tmp, "out"), str(h["norm_eps"])]
+        env = dict(os.environ, REF_BLAS_THREADS=str(cores), OPENBLAS_NUM_THREADS=str(cores))
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True)
+        if r.returncode != 0:
+            return None, cores, "ref_harness failed: " + (r.stderr.strip().splitlines() or ["?"])[-1], "reference"
+        ms = np.loadtxt(os.path.join(tmp, "out_time.txt"), ndmin=1)
+    ms = ms[warmup:] if len(ms) > warmup else ms
+    tok_s = sample_B * T / (float(np.mean(ms)) / 1e3)
+    desc = "%s model, %d sequence(s) of %d tokens per step, %d timed steps, weights at their init defaults (zeros / gamma=1), OpenBLAS threads=%d, elementwise code single-threaded" % (
+        workload, sample_B, T, len(ms), cores)
+    return tok_s, cores, desc, "reference"
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    arch, V, T, C, H, L, F, B, accum = WORKLOADS[args.workload]
+    t0 = time.time()
+    # each step is ~1.3 TFLOP of CPU work on the bounded sample: two timed steps after one warm-up keep the run within minutes
+    tok_s, cores, desc, kind = reference_cpu_run(args.workload, min(args.steps, 2), min(args.warmup, 1))
+    if tok_s is None:
+        print(json.dumps({"impl": "reference", "unavailable": desc}))
+        return
+    line = {
+        "impl": "reference", "metric": "GPT fp32 train tokens/s (fwd+bwd+AdamW)", "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * T / tok_s, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic Zipf(1.1) tokens",
+        "config": {"workload": args.workload, "arch": arch, "layers": L, "d_model": C, "heads": H, "d_ff": F, "seq_len": T, "vocab": V, "sample": desc},
+        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": desc},
+        "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.time() - t0,
+    }
+    print(json.dumps(line))
+
+
+# ---- our arm ----------------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import numpy as np
+    import torch
+
+    from gradcraft_b200 import capi, synth
+    from gradcraft_b200.trainer import Trainer
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the training path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    arch, V, T, C, H, L, F, B, accum = WORKLOADS[args.workload]
+    K, W = args.steps, args.warmup
+    pk = peaks()
+
+    tr = Trainer(arch, V, T, C, H, L, F, lr=HYPER["lr"], beta1=HYPER["beta1"], beta2=HYPER["beta2"], wd=HYPER["wd"], eps=HYPER["eps"], norm_eps=HYPER["norm_eps"], ce_eps=HYPER["ce_eps"],
+                 clip=0.0, device=local_rank)
+    tr.load(synth.gpt_weights(arch, V, T, C, H, L, F, seed=0))  # identical on every rank
+    lib = capi.lib()
+    ctx = tr.context()
+    if world > 1:
+        uid = torch.zeros(capi.DP_ID_BYTES, dtype=torch.uint8)
+        if rank == 0:
+            buf = np.zeros(capi.DP_ID_BYTES, np.uint8)
+            lib.dp_unique_id(buf)
+            uid = torch.from_numpy(buf)
+        uid = uid.cuda()
+        dist.broadcast(uid, 0)
+        tr.dp_init(uid.cpu().numpy(), rank, world, accum)
+
+    # token streams: rank r draws from seed base + r; W + K steps of `accum` micro-batches, twice (device-resident pass, host pass)
+    n_mb = (W + K) * accum
+    host = torch.from_numpy(synth.token_batches(1000 + rank, n_mb, B, T, V)).pin_memory()
+    resident = host.cuda()
+    stream = torch.cuda.ExternalStream(tr.stream(), device=local_rank)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_step(i, src, on_device, want_loss):
+        tr.zero_grad()
+        loss = 0.0
+        for mb in range(accum):
+            x, y = src[i * accum + mb, 0], src[i * accum + mb, 1]
+            l = tr.forward_backward(x, y, accum, want_loss, on_device)
+            loss += l if want_loss else 0.0
+        tr.optimizer_step()
+        return loss
+
+    def timed(src, on_device, want_loss, profile_gemm):
+        for i in range(W):
+            one_step(i, src, on_device, want_loss)
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        launches0 = tr.launch_count()
+        if profile_gemm:
+            lib.profile_gemm_begin(ctx)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        last = 0.0
+        for i in range(W, W + K):
+            last = one_step(i, src, on_device, want_loss)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        prof = None
+        if profile_gemm:
+            import ctypes
+
+            n, tms, fl = ctypes.c_int64(), ctypes.c_double(), ctypes.c_double()
+            lib.profile_gemm_end(ctx, ctypes.byref(n), ctypes.byref(tms), ctypes.byref(fl))
+            prof = (n.value, tms.value, fl.value)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, clocks, tr.launch_count() - launches0, prof, last
+
+    ms_dev, clocks, launches, prof, _ = timed(resident, True, False, True)
+    ms_e2e, _, _, _, last_loss = timed(host, False, True, False)
+    engine = lib.ctx_last_gemm_engine(ctx)
+    tokens_per_step = B * T * accum * world
+    value = tokens_per_step * K / (ms_dev / 1e3)
+    e2e = tokens_per_step * K / (ms_e2e / 1e3)
+    n_gemm, gemm_ms, gemm_flops = prof
+    achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
+    fpt = flops_per_token(V, T, C, L, F)
+    hwm = tr.high_water_bytes()
+    nparams = tr.num_params()
+    nbuckets = tr.num_buckets()
+    tr.close()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tok_s, cores, desc, kind = reference_cpu_run(args.workload, 1, 1)
+        cpu = {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": desc}
+    if rank == 0:
+        line = {
+            "metric": "GPT fp32 train tokens/s (fwd+bwd+AdamW)", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_dev / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic: Zipf(1.1) tokens (seed 1000+rank), N(0,0.02) weights (seed 0)",
+            "config": {"workload": args.workload, "arch": arch, "layers": L, "d_model": C, "heads": H, "d_ff": F, "seq_len": T, "vocab": V, "batch_per_gpu": B, "micro_batches_per_step": accum,
+                       "global_batch": B * accum * world, "params": nparams, "parallelism": "dp%d" % world, "gradient_buckets": nbuckets,
+                       "l2": "working set per step (%.1f GB arena high-water) far exceeds the 126 MB L2" % (hwm / 1e9), "gemm_engine": {1: "simt_fp32", 2: "tcgen05_3xtf32"}.get(engine, "none"),
+                       "algorithmic_gflop_per_token": fpt / 1e9, "step_tflops": fpt * tokens_per_step / world / (ms_dev / K / 1e3) / 1e12},
+            "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8 * accum, "d2h_bytes_per_step": 4 * accum, "ms_per_step": ms_e2e / K, "last_loss": last_loss},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tensor_tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tensor_tflops"], "traffic": None,
+                         "kernel": "gemm (%d launches, %.1f ms of the timed region)" % (n_gemm, gemm_ms), "peak_source": "%s dense bf16, sustained; 3xTF32 issues 3 tf32 MMAs per product, so its ceiling is 1/6 of this" % pk["source"],
+                         "gemm_share_of_step": gemm_ms / ms_dev},
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# ---- fused backward kernels vs the HBM roofline -----------------------------------------------------------------------
+def run_kernels(args):
+    import numpy as np
+    import torch
+
+    from gradcraft_b200 import capi
+
+    ctx = capi.Context(0)
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timeit(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        ts = []
+        for _ in range(max(5, args.steps)):
+            flush.zero_()  # evict L2 between timed launches
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        return float(np.median(ts))
+
+    out = {}
+    M, V = 16384, 32768
+    P = torch.rand(M, V, device="cuda")
+    P /= P.sum(-1, keepdim=True)
+    Tg = torch.randint(0, V, (M,), dtype=torch.int32, device="cuda")
+    ms = timeit(lambda: ctx.softmax_ce_bwd_f32(P, P, Tg, capi.IDX_I32, 1.0, M, V, 0))
+    out["softmax_ce_bwd [16384,32768]"] = (ms, 2 * M * V * 4 + M * 4)
+    del P
+    M, C = 16384, 1024
+    x, dy, g, b = torch.randn(M, C, device="cuda"), torch.randn(M, C, device="cuda") * 1e-2, torch.ones(C, device="cuda"), torch.zeros(C, device="cuda")
+    y, mu, rs, dx, dg, db = torch.empty_like(x), torch.empty(M, device="cuda"), torch.empty(M, device="cuda"), torch.empty_like(x), torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
+    ctx.layernorm_fwd_f32(y, mu, rs, x, g, b, M, C, 1e-5)
+    ms = timeit(lambda: ctx.layernorm_bwd_f32(dx, dg, db, dy, x, g, mu, rs, M, C, 0, 0))
+    out["layernorm_bwd [16384,1024]"] = (ms, 3 * M * C * 4 + 2 * M * 4 + 3 * C * 4)
+    M, F = 16384, 4096
+    x, dy = torch.randn(M, F, device="cuda"), torch.randn(M, F, device="cuda") * 1e-2
+    dx = torch.empty_like(x)
+    ms = timeit(lambda: ctx.gelu_bwd_f32(dx, dy, x, M * F, 0))
+    out["gelu_bwd [16384,4096]"] = (ms, 3 * M * F * 4)
+    del x, dy, dx
+    Bn, H, T = 16, 16, 1024
+    rows = Bn * H * T
+    S = torch.randn(rows, T, device="cuda")
+    ctx.causal_softmax_fwd_f32(S, S, 0.125, rows, T)
+    dP = torch.randn(rows, T, device="cuda") * 1e-2
+    ms = timeit(lambda: ctx.causal_softmax_bwd_f32(dP, dP, S, 0.125, rows, T, 0))
+    out["causal_softmax_bwd [16,16,1024,1024]"] = (ms, 4 * Bn * H * T * (2 * (T + 1) // 2 + T))
+    ctx.sync()
+    kernels = {k: {"ms": ms, "algorithmic_bytes": by, "achieved_gbs": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / pk["hbm_gbs"]} for k, (ms, by) in out.items()}
+    worst = min(kernels.values(), key=lambda d: d["frac_of_hbm_peak"])
+    print(json.dumps({"metric": "fused backward kernels, achieved HBM GB/s vs measured peak", "value": worst["frac_of_hbm_peak"], "unit": "fraction of HBM peak (worst kernel)", "n_gpus": 1,
+                      "steps": max(5, args.steps), "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "f32", "data": "synthetic N(0,1) activations, N(0,1e-2) upstream gradients",
+                      "config": {"workload": "kernels", "l2": "flushed between timed launches (256 MB write)"}, "peak_hbm_gbs": pk["hbm_gbs"], "peak_source": pk["source"], "kernels": kernels}))
+    ctx.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gpt180m", choices=list(WORKLOADS) + ["kernels"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if args.workload == "kernels":
+        run_kernels(args)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

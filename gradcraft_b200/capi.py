@@ -19,7 +19,7 @@ OP_N, OP_T = 0, 1
 ADAMW_CHUNK = 1024
 DP_ID_BYTES = 128
 
-_SCALARS = {"int": ctypes.c_int, "int64_t": ctypes.c_int64, "float": ctypes.c_float, "size_t": ctypes.c_size_t}
+_SCALARS = {"int": ctypes.c_int, "int64_t": ctypes.c_int64, "float": ctypes.c_float, "size_t": ctypes.c_size_t, "double": ctypes.c_double}
 
 
 class GcbError(RuntimeError):

@@ -68,6 +68,11 @@ struct gcb_ctx {
     void* nccl_comm = nullptr;
     int dp_rank = 0, dp_world = 1;
     void* tma_encode = nullptr;  // cuTensorMapEncodeTiled, resolved lazily
+    // optional timing of every GEMM launch with CUDA events on the compute stream
+    bool prof_on = false;
+    std::vector<cudaEvent_t> prof_events;
+    size_t prof_used = 0;
+    double prof_flops = 0.0;
     std::mutex mu;
 };
 

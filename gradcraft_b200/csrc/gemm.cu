@@ -13,15 +13,27 @@ static int run_gemm(gcb_ctx* ctx, int op_a, int op_b, const GemmArgs& g, const c
     const bool ta = op_a == GCB_OP_T, tb = op_b == GCB_OP_T;
     GCB_REQUIRE(g.lda >= (ta ? g.M : g.K) && g.ldb >= (tb ? g.K : g.N) && g.ldc >= g.N, "%s: leading dimension smaller than the row length (lda %lld ldb %lld ldc %lld)", who,
                 (long long)g.lda, (long long)g.ldb, (long long)g.ldc);
-    if (ctx->gemm_engine != 1 && gemm_tc_eligible(ta, tb, g)) {
-        int rc = gemm_tc_launch(ctx, ta, tb, g);
-        if (rc != GCB_UNSUPPORTED) return rc;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (ctx->prof_on) {
+        if (ctx->prof_used + 2 > ctx->prof_events.size()) {
+            for (int i = 0; i < 512; ++i) { cudaEvent_t e; GCB_CHECK_CUDA(cudaEventCreate(&e)); ctx->prof_events.push_back(e); }
+        }
+        e0 = ctx->prof_events[ctx->prof_used++];
+        e1 = ctx->prof_events[ctx->prof_used++];
+        ctx->prof_flops += 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)(g.batch_outer * g.batch_inner);
+        GCB_CHECK_CUDA(cudaEventRecord(e0, ctx->stream));
     }
-    if (ctx->gemm_engine == 2) {
-        set_error("%s: the tcgen05 engine was forced but cannot take these operands (alignment / leading dimensions)", who);
-        return GCB_UNSUPPORTED;
+    int rc = GCB_UNSUPPORTED;
+    if (ctx->gemm_engine != 1 && gemm_tc_eligible(ta, tb, g)) rc = gemm_tc_launch(ctx, ta, tb, g);
+    if (rc == GCB_UNSUPPORTED) {
+        if (ctx->gemm_engine == 2) {
+            set_error("%s: the tcgen05 engine was forced but cannot take these operands (alignment / leading dimensions)", who);
+            return GCB_UNSUPPORTED;
+        }
+        rc = gemm_simt_launch(ctx, ta, tb, g);
     }
-    return gemm_simt_launch(ctx, ta, tb, g);
+    if (e1) GCB_CHECK_CUDA(cudaEventRecord(e1, ctx->stream));
+    return rc;
 }
 
 extern "C" {
@@ -39,6 +51,30 @@ int gcb_gemm_batched_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N,
     GCB_REQUIRE(batch_outer >= 0 && batch_inner >= 0, "gcb_gemm_batched_f32: negative batch count");
     GemmArgs g{M, N, K, alpha, beta, A, B, nullptr, C, lda, ldb, ldc, a_so, a_si, b_so, b_si, c_so, c_si, batch_outer, batch_inner};
     return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_batched_f32");
+}
+
+int gcb_profile_gemm_begin(gcb_ctx* ctx) {
+    GCB_REQUIRE(ctx, "gcb_profile_gemm_begin: ctx is NULL");
+    ctx->prof_on = true;
+    ctx->prof_used = 0;
+    ctx->prof_flops = 0.0;
+    return GCB_OK;
+}
+
+int gcb_profile_gemm_end(gcb_ctx* ctx, int64_t* launches, double* total_ms, double* total_flops) {
+    GCB_REQUIRE(ctx, "gcb_profile_gemm_end: ctx is NULL");
+    ctx->prof_on = false;
+    GCB_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    double ms = 0.0;
+    for (size_t i = 0; i + 1 < ctx->prof_used; i += 2) {
+        float t = 0.0f;
+        GCB_CHECK_CUDA(cudaEventElapsedTime(&t, ctx->prof_events[i], ctx->prof_events[i + 1]));
+        ms += t;
+    }
+    if (launches) *launches = (int64_t)(ctx->prof_used / 2);
+    if (total_ms) *total_ms = ms;
+    if (total_flops) *total_flops = ctx->prof_flops;
+    return GCB_OK;
 }
 
 }  // extern "C"

@@ -131,6 +131,12 @@ GCB_API int gcb_gemm_batched_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, in
                          float beta, float* C, int64_t ldc, int64_t c_stride_outer, int64_t c_stride_inner,
                          int64_t batch_outer, int64_t batch_inner);
 
+/* Measurement aid (the reference times with std::chrono around whole loops, benchmarks/bench_kernels.cpp:10-27):
+ * between begin and end every GEMM launch is bracketed by CUDA events on the compute stream; end synchronises and
+ * returns the number of launches, their summed device time and their algorithmic FLOPs (2*M*N*K*batches). */
+GCB_API int gcb_profile_gemm_begin(gcb_ctx* ctx);
+GCB_API int gcb_profile_gemm_end(gcb_ctx* ctx, int64_t* launches, double* total_ms, double* total_flops);
+
 /* ---- embedding: CUDAMath::apply_embed / apply_scatter_add, cuda_math.hpp:29-32 ------------------ */
 GCB_API int gcb_embed_f32(gcb_ctx* ctx, float* out, const void* indices, int index_type, const float* table, int64_t n_indices, int64_t width, int64_t vocab);
 /* dtable[idx[i], :] += dy[i, :].  Deterministic: positions are counting-sorted by row (stable) and each
