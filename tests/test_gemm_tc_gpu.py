@@ -1,0 +1,107 @@
+"""The tcgen05 3xTF32 GEMM engine against float64 numpy: every operand layout, tile width, ragged edges, bias / beta
+epilogues, head-strided batches and split-K.  Tolerance: max-abs-rel 2e-5 per output (fp32-class accuracy; plain TF32
+would sit near 1e-3)."""
+import numpy as np
+import pytest
+
+from tests.helpers import max_abs_rel
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-5
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+
+    from gradcraft_b200 import capi
+
+    ctx = capi.Context(0)
+    ctx.ctx_set_gemm_engine(2)
+    yield ctx, torch, capi
+    ctx.ctx_set_gemm_engine(0)
+    ctx.sync()
+    ctx.close()
+
+
+def rnd(seed, *shape):
+    return np.random.default_rng(seed).standard_normal(shape, dtype=np.float32)
+
+
+@pytest.mark.parametrize("opa,opb,M,N,K", [
+    (0, 1, 128, 64, 64), (0, 0, 128, 256, 32), (1, 0, 128, 128, 48), (1, 1, 128, 64, 16),
+    (0, 0, 300, 520, 100), (0, 1, 257, 1000, 132), (1, 0, 200, 72, 1028), (1, 1, 130, 260, 36),
+    (0, 0, 1024, 1024, 1024), (1, 0, 512, 512, 8192),
+])
+def test_tc_gemm_vs_numpy(env, opa, opb, M, N, K):
+    ctx, torch, capi = env
+    A = rnd(1, *((K, M) if opa else (M, K)))
+    B = rnd(2, *((N, K) if opb else (K, N)))
+    C0, bias = rnd(3, M, N), rnd(4, N)
+    dA, dB, dbias = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), torch.from_numpy(bias).cuda()
+    a = (A.T if opa else A).astype(np.float64)
+    b = (B.T if opb else B).astype(np.float64)
+    C = torch.from_numpy(C0).cuda()
+    ctx.gemm_f32(opa, opb, M, N, K, 1.0, dA, A.shape[1], dB, B.shape[1], 0.0, C, N, None)
+    ctx.sync()
+    assert ctx.ctx_last_gemm_engine() == 2
+    assert max_abs_rel(C.cpu().numpy(), a @ b) < TOL
+    C = torch.from_numpy(C0).cuda()
+    ctx.gemm_f32(opa, opb, M, N, K, 0.5, dA, A.shape[1], dB, B.shape[1], 1.0, C, N, dbias)
+    ctx.sync()
+    assert max_abs_rel(C.cpu().numpy(), 0.5 * (a @ b) + C0 + bias) < TOL
+
+
+def test_tc_gemm_is_fp32_class_not_tf32_class(env):
+    """Values with long mantissas: a single TF32 product would lose ~1e-3; the split engine must not."""
+    ctx, torch, capi = env
+    M = N = K = 256
+    A = (1.0 + rnd(5, M, K) * 1e-3).astype(np.float32)
+    B = (1.0 + rnd(6, K, N) * 1e-3).astype(np.float32)
+    C = torch.empty(M, N, device="cuda")
+    ctx.gemm_f32(0, 0, M, N, K, 1.0, torch.from_numpy(A).cuda(), K, torch.from_numpy(B).cuda(), N, 0.0, C, N, None)
+    ctx.sync()
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    assert float(np.abs(C.cpu().numpy() - ref).max() / np.abs(ref).max()) < 2e-6
+
+
+def test_tc_gemm_head_strided_batches(env):
+    """q k^T and p v on (B, T, H*D) buffers addressed through two-level batch strides, output written head-interleaved."""
+    ctx, torch, capi = env
+    Bn, H, T, D = 2, 3, 160, 64
+    C = H * D
+    q, k, v = rnd(7, Bn, T, C), rnd(8, Bn, T, C), rnd(9, Bn, T, C)
+    Q, Kd, Vd = (torch.from_numpy(x).cuda() for x in (q, k, v))
+    S = torch.empty(Bn * H, T, T, device="cuda")
+    ctx.gemm_batched_f32(0, 1, T, T, D, 1.0, Q, C, T * C, D, Kd, C, T * C, D, 0.0, S, T, H * T * T, T * T, Bn, H)
+    ctx.sync()
+    qh = q.reshape(Bn, T, H, D).transpose(0, 2, 1, 3).astype(np.float64)
+    kh = k.reshape(Bn, T, H, D).transpose(0, 2, 1, 3).astype(np.float64)
+    vh = v.reshape(Bn, T, H, D).transpose(0, 2, 1, 3).astype(np.float64)
+    ref_s = qh @ kh.transpose(0, 1, 3, 2)
+    assert max_abs_rel(S.cpu().numpy().reshape(Bn, H, T, T), ref_s) < TOL
+    O = torch.zeros(Bn, T, C, device="cuda")
+    ctx.gemm_batched_f32(0, 0, T, D, T, 1.0, S, T, H * T * T, T * T, Vd, C, T * C, D, 0.0, O, C, T * C, D, Bn, H)
+    ctx.sync()
+    ref_o = (S.cpu().numpy().reshape(Bn, H, T, T).astype(np.float64) @ vh).transpose(0, 2, 1, 3).reshape(Bn, T, C)
+    assert max_abs_rel(O.cpu().numpy(), ref_o) < TOL
+    dV = torch.zeros(Bn, T, C, device="cuda")  # P^T . dO with A transposed
+    ctx.gemm_batched_f32(1, 0, T, D, T, 1.0, S, T, H * T * T, T * T, Q, C, T * C, D, 0.0, dV, C, T * C, D, Bn, H)
+    ctx.sync()
+    ref_dv = (S.cpu().numpy().reshape(Bn, H, T, T).astype(np.float64).transpose(0, 1, 3, 2) @ qh).transpose(0, 2, 1, 3).reshape(Bn, T, C)
+    assert max_abs_rel(dV.cpu().numpy(), ref_dv) < TOL
+
+
+def test_unaligned_operands_fall_back_or_fail_loudly(env):
+    ctx, torch, capi = env
+    A, B = rnd(10, 64, 130), rnd(11, 130, 66)  # ld 130 / 66: not multiples of four floats
+    C = torch.empty(64, 66, device="cuda")
+    with pytest.raises(capi.GcbError) as e:  # engine forced to tcgen05: must refuse, not silently take another path
+        ctx.gemm_f32(0, 0, 64, 66, 130, 1.0, torch.from_numpy(A).cuda(), 130, torch.from_numpy(B).cuda(), 66, 0.0, C, 66, None)
+    assert e.value.status == capi.UNSUPPORTED
+    ctx.ctx_set_gemm_engine(0)
+    ctx.gemm_f32(0, 0, 64, 66, 130, 1.0, torch.from_numpy(A).cuda(), 130, torch.from_numpy(B).cuda(), 66, 0.0, C, 66, None)
+    ctx.sync()
+    assert ctx.ctx_last_gemm_engine() == 1
+    assert max_abs_rel(C.cpu().numpy(), A.astype(np.float64) @ B.astype(np.float64)) < 1e-5
+    ctx.ctx_set_gemm_engine(2)
