@@ -11,7 +11,8 @@
 // accumulator, so the dropped term is small*small ~ 2^-22 of the product.
 // Shared-memory layouts are the canonical UMMA ones the TMA swizzle modes produce:
 //   operand contiguous along K   -> rows of 64 B, SWIZZLE_64B, descriptor "K-major",  SBO = 512 B, +32 B per K=8 step
-//   operand contiguous along M/N -> 32-float chunks x 16 k-rows, SWIZZLE_128B, "MN-major", LBO = 2 KB (chunk), SBO = 1 KB
+//   operand contiguous along M/N -> 32-float chunks x 16 k-rows, 128-byte swizzle in 32-byte units (the only MN-major
+//                                   layout TF32 accepts), "MN-major", LBO = 2 KB (next chunk), SBO = 512 B (next 4 k-rows)
 // Every mbarrier wait is bounded; a wait that runs out sets the context's status word and the kernel drains and exits
 // (TMEM is always released), so a logic error cannot hang the device.
 // Split-K (deterministic): when a problem has too few tiles to fill 148 SMs, K is cut into slices whose partial tiles go
@@ -68,7 +69,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes,
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= (uint64_t)1 << 46;       // descriptor version of this architecture
-    d |= (uint64_t)layout << 61;  // 2 = 128-byte swizzle, 4 = 64-byte swizzle
+    d |= (uint64_t)layout << 61;  // 1 = 128-byte swizzle in 32-byte units, 2 = 128-byte swizzle, 4 = 64-byte swizzle
     return d;
 }
 __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -181,10 +182,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
 #pragma unroll
                 for (int j = 0; j < TC_BK / 8; ++j) {
                     const uint32_t a_off = A_MN ? j * 1024 : j * 32, b_off = B_MN ? j * 1024 : j * 32;
-                    const uint64_t a_big = A_MN ? make_desc(sa + a_off, 2048, 1024, 2) : make_desc(sa + a_off, 16, 512, 4);
-                    const uint64_t a_sml = A_MN ? make_desc(sa + S::A_BYTES + a_off, 2048, 1024, 2) : make_desc(sa + S::A_BYTES + a_off, 16, 512, 4);
-                    const uint64_t b_big = B_MN ? make_desc(sb + b_off, 2048, 1024, 2) : make_desc(sb + b_off, 16, 512, 4);
-                    const uint64_t b_sml = B_MN ? make_desc(sb + S::B_BYTES + b_off, 2048, 1024, 2) : make_desc(sb + S::B_BYTES + b_off, 16, 512, 4);
+                    const uint64_t a_big = A_MN ? make_desc(sa + a_off, 2048, 512, 1) : make_desc(sa + a_off, 16, 512, 4);
+                    const uint64_t a_sml = A_MN ? make_desc(sa + S::A_BYTES + a_off, 2048, 512, 1) : make_desc(sa + S::A_BYTES + a_off, 16, 512, 4);
+                    const uint64_t b_big = B_MN ? make_desc(sb + b_off, 2048, 512, 1) : make_desc(sb + b_off, 16, 512, 4);
+                    const uint64_t b_sml = B_MN ? make_desc(sb + S::B_BYTES + b_off, 2048, 512, 1) : make_desc(sb + S::B_BYTES + b_off, 16, 512, 4);
                     umma_tf32(tmem_base, a_sml, b_big, idesc, (i | j) ? 1u : 0u);  // small terms first: they are added to a small running sum
                     umma_tf32(tmem_base, a_big, b_sml, idesc, 1u);
                     umma_tf32(tmem_base, a_big, b_big, idesc, 1u);
@@ -322,7 +323,7 @@ static bool encode_operand(EncodeTiledFn enc, CUtensorMap* map, const float* ptr
     cuuint32_t box[4] = {mn_major ? 32u : (cuuint32_t)TC_BK, mn_major ? (cuuint32_t)TC_BK : (cuuint32_t)tile_rows, 1u, 1u};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 

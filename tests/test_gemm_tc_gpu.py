@@ -29,7 +29,7 @@ def rnd(seed, *shape):
 
 
 @pytest.mark.parametrize("opa,opb,M,N,K", [
-    (0, 1, 128, 64, 64), (0, 0, 128, 256, 32), (1, 0, 128, 128, 48), (1, 1, 128, 64, 16),
+    (0, 1, 128, 64, 64), (0, 0, 128, 256, 32), (1, 0, 128, 128, 48), (1, 1, 128, 128, 16),
     (0, 0, 300, 520, 100), (0, 1, 257, 1000, 132), (1, 0, 200, 72, 1028), (1, 1, 130, 260, 36),
     (0, 0, 1024, 1024, 1024), (1, 0, 512, 512, 8192),
 ])
