@@ -194,4 +194,41 @@ int gct_dp_init(gct_trainer* tr, const uint8_t* id128, int rank, int world, int6
     });
 }
 
+// Host-only: replays the bucket bookkeeping of the backward sweep for `steps` optimizer steps of `accum` micro-batches and
+// records every bucket reduction as (step, micro_batch, slot after which it fired or -1 for the consumer-side sync, bucket,
+// begin, count).  No GPU is touched; tests drive a host all-reduce with the recorded ranges.
+int gct_dp_simulate(const int64_t* sizes, int64_t n_slots, int64_t bucket_elems, int world, int64_t accum_hint, int64_t accum, int64_t steps, int64_t* events, int64_t max_events,
+                    int64_t* n_events, int64_t* total_elems) {
+    return guarded([&] {
+        ParamArena a;
+        a.device = Device(DeviceType::CPU);
+        std::vector<std::tuple<std::string, int64_t, bool>> plan;
+        for (int64_t i = 0; i < n_slots; ++i) plan.emplace_back("p" + std::to_string(i), sizes[i], false);
+        a.plan(plan, bucket_elems, GCB_ADAMW_CHUNK);
+        a.dp_world = world;
+        a.accum_expected = accum_hint;
+        int64_t count = 0, cur_step = 0, cur_mb = 0, cur_slot = -1;
+        a.reduce_hook = [&](int k, int64_t begin, int64_t n) {
+            if (count < max_events) {
+                int64_t* e = events + 6 * count;
+                e[0] = cur_step; e[1] = cur_mb; e[2] = cur_slot; e[3] = k; e[4] = begin; e[5] = n;
+            }
+            ++count;
+        };
+        a.wait_hook = [] {};
+        for (cur_step = 0; cur_step < steps; ++cur_step) {
+            a.on_zero_grad();
+            for (cur_mb = 0; cur_mb < accum; ++cur_mb) {
+                a.begin_backward();
+                for (cur_slot = 0; cur_slot < n_slots; ++cur_slot) { a.slots[cur_slot].grad_live = true; a.mark_final((int)cur_slot); }
+            }
+            cur_slot = -1;
+            cur_mb = accum;
+            a.sync_gradients();
+        }
+        if (n_events) *n_events = count;
+        if (total_elems) *total_elems = a.total;
+    });
+}
+
 }  // extern "C"

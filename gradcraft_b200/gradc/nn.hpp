@@ -179,26 +179,10 @@ public:
             std::reverse(ordered.begin(), ordered.end());
             auto arena = std::make_shared<ParamArena>();
             arena->device = device;
-            const int64_t bucket_cap = bucket_elems();
-            int64_t off = 0, bucket_begin = 0;
-            for (auto& [name, p] : ordered) {
-                ParamArena::Slot s;
-                s.name = name;
-                s.size = p->tensor().volume();
-                s.padded = (s.size + GCB_ADAMW_CHUNK - 1) / GCB_ADAMW_CHUNK * GCB_ADAMW_CHUNK;
-                s.offset = off;
-                s.no_decay = p->no_decay();
-                s.bucket = (int)arena->buckets.size();
-                off += s.padded;
-                arena->slots.push_back(s);
-                if (off - bucket_begin >= bucket_cap) {
-                    arena->buckets.push_back({bucket_begin, off, 0, 0, false});
-                    bucket_begin = off;
-                }
-            }
-            if (off > bucket_begin || arena->buckets.empty()) arena->buckets.push_back({bucket_begin, off, 0, 0, false});
-            for (auto& s : arena->slots) arena->buckets[s.bucket].n_slots++;
-            arena->total = off;
+            std::vector<std::tuple<std::string, int64_t, bool>> plan;
+            for (auto& [name, p] : ordered) plan.emplace_back(name, p->tensor().volume(), p->no_decay());
+            arena->plan(plan, bucket_elems(), GCB_ADAMW_CHUNK);
+            const int64_t off = arena->total;
             Backend& be = Backend::get();
             gcb_ctx* c = be.ctx(device);
             arena->w = static_cast<float*>(be.allocate(off * (int64_t)sizeof(float), device));

@@ -18,6 +18,7 @@
 #include <algorithm>
 #include <functional>
 #include <memory>
+#include <tuple>
 #include <unordered_set>
 
 #include "runtime.hpp"
@@ -102,6 +103,35 @@ struct ParamArena {
     bool overlap_active = false;  // this backward() is the last of the step: buckets may be reduced as they finish
     bool reduced_this_step = false;
 
+    // Host-side stand-ins for the collective (tests of the bucket logic without a GPU): when set they replace the NCCL calls.
+    std::function<void(int bucket, int64_t begin, int64_t n)> reduce_hook;
+    std::function<void()> wait_hook;
+
+    // Lays slots out in the given order (each padded to `chunk` elements) and cuts buckets of at least `bucket_cap` elements.
+    void plan(const std::vector<std::tuple<std::string, int64_t, bool>>& params, int64_t bucket_cap, int64_t chunk) {
+        slots.clear();
+        buckets.clear();
+        int64_t off = 0, bucket_begin = 0;
+        for (const auto& [name, size, no_decay] : params) {
+            Slot s;
+            s.name = name;
+            s.size = size;
+            s.padded = (size + chunk - 1) / chunk * chunk;
+            s.offset = off;
+            s.no_decay = no_decay;
+            s.bucket = (int)buckets.size();
+            off += s.padded;
+            slots.push_back(s);
+            if (off - bucket_begin >= bucket_cap) {
+                buckets.push_back({bucket_begin, off, 0, 0, false});
+                bucket_begin = off;
+            }
+        }
+        if (off > bucket_begin || buckets.empty()) buckets.push_back({bucket_begin, off, 0, 0, false});
+        for (auto& s : slots) buckets[s.bucket].n_slots++;
+        total = off;
+    }
+
     ~ParamArena() {
         Backend& b = Backend::get();
         b.release(w, device); b.release(g, device); b.release(m, device); b.release(v, device); b.release(decay_mask, device);
@@ -123,7 +153,8 @@ struct ParamArena {
     void reduce_bucket(int k) {
         Bucket& b = buckets[k];
         if (b.reduced) return;
-        gcb_check(gcb_dp_allreduce_avg_f32(Backend::get().ctx(device), g + b.begin, b.end - b.begin), "gradient all-reduce");
+        if (reduce_hook) reduce_hook(k, b.begin, b.end - b.begin);
+        else gcb_check(gcb_dp_allreduce_avg_f32(Backend::get().ctx(device), g + b.begin, b.end - b.begin), "gradient all-reduce");
         b.reduced = true;
     }
     // Gradient consumers (clip, optimizer) call this: reduces whatever has not been reduced yet and makes the
@@ -132,7 +163,8 @@ struct ParamArena {
         if (dp_world <= 1 || reduced_this_step) return;
         if (accum_expected == 0) accum_expected = backward_calls;  // learnt on the first step
         for (int k = 0; k < (int)buckets.size(); ++k) reduce_bucket(k);
-        gcb_check(gcb_dp_wait(Backend::get().ctx(device)), "waiting for the gradient all-reduce");
+        if (wait_hook) wait_hook();
+        else gcb_check(gcb_dp_wait(Backend::get().ctx(device)), "waiting for the gradient all-reduce");
         reduced_this_step = true;
     }
     void on_zero_grad() {

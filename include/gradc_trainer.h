@@ -43,6 +43,10 @@ GCT_API int64_t gct_arena_high_water_bytes(gct_trainer* tr);
 GCT_API int64_t gct_num_buckets(gct_trainer* tr);
 /* data parallel: id from gcb_dp_unique_id (rank 0) broadcast by the launcher */
 GCT_API int gct_dp_init(gct_trainer* tr, const uint8_t* id128, int rank, int world, int64_t accum_steps);
+/* Host-only replay of the gradient-bucket bookkeeping (no GPU): events are rows of 6 int64
+ * (step, micro_batch, slot after which the reduction fired or -1 when the gradient consumer forced it, bucket, begin, count). */
+GCT_API int gct_dp_simulate(const int64_t* slot_sizes, int64_t n_slots, int64_t bucket_elems, int world, int64_t accum_hint, int64_t accum, int64_t steps, int64_t* events,
+                            int64_t max_events, int64_t* n_events, int64_t* total_elems);
 #ifdef __cplusplus
 }
 #endif

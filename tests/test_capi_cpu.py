@@ -43,3 +43,18 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".hpp", ".h")):
                 text = open(os.path.join(dirpath, f), errors="ignore").read()
                 assert "oracle" not in text.lower(), os.path.join(dirpath, f)
+
+
+def test_reference_train_cpp_compiles_unchanged_against_the_host_api(tmp_path):
+    """train.cpp of the reference, byte for byte, must build against gradcraft_b200/gradc (syntax + semantic check only)."""
+    import shutil
+    import subprocess
+
+    src = "/root/reference/train.cpp"
+    if not os.path.exists(src):
+        pytest.skip("reference tree not present on this machine")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    shutil.copy(src, tmp_path / "train.cpp")  # a quoted include searches the including file's directory first
+    r = subprocess.run(["g++", "-std=c++23", "-fsyntax-only", "-I", os.path.join(root, "gradcraft_b200"), "-I", "/usr/local/cuda/include", str(tmp_path / "train.cpp")],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
