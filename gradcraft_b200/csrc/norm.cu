@@ -320,11 +320,66 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
     return GCB_OK;
 }
 
+// ---- LayerNorm backward for callers that must not allocate ---------------------------------------------------
+// The per-CTA dgamma / dbeta partial sums of the fast path normally sit in a block taken from the context's arena.
+// Here they sit in this fixed device array instead, so the call touches no allocator at all.  Every GPU that loads the
+// library carries the array (kNoAllocFloats * 4 bytes = 3.5 MiB) until the process exits.
+constexpr int kNoAllocMaxCols = 1024;
+constexpr int kNoAllocMaxBlocks = kSMs * 3;
+constexpr size_t kNoAllocFloats = (size_t)kNoAllocMaxBlocks * 2 * kNoAllocMaxCols;
+static __device__ __align__(256) float g_ln_bwd_partials[kNoAllocFloats];
+// In host code the array's name is only a handle for the runtime, not a device address; the real address is looked
+// up once per device and kept here.
+static float* g_ln_bwd_partials_addr[64] = {};
+static std::mutex g_ln_bwd_partials_mu;
+
+static int noalloc_scratch(int device, float** out) {
+    GCB_REQUIRE(device >= 0 && device < 64, "gcb_layernorm_bwd_noalloc_f32: device index %d is outside the supported range", device);
+    std::lock_guard<std::mutex> lk(g_ln_bwd_partials_mu);
+    if (!g_ln_bwd_partials_addr[device]) {
+        GCB_CHECK_CUDA(cudaSetDevice(device));
+        float* p = nullptr;
+        GCB_CHECK_CUDA(cudaGetSymbolAddress((void**)&p, g_ln_bwd_partials));
+        g_ln_bwd_partials_addr[device] = p;
+    }
+    *out = g_ln_bwd_partials_addr[device];
+    return GCB_OK;
+}
+
 }  // namespace gcb
 
 using namespace gcb;
 
 extern "C" {
+
+int gcb_layernorm_bwd_noalloc_f32(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const float* dy, const float* x, const float* gamma, const float* mean, const float* rstd,
+                                  int64_t rows, int64_t cols, int acc_dx, int acc_params) {
+    GCB_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (dy && x && gamma && mean && rstd)), "gcb_layernorm_bwd_noalloc_f32: bad arguments");
+    GCB_REQUIRE(cols > 0 && rows > 0, "gcb_layernorm_bwd_noalloc_f32: empty input (rows %lld, cols %lld)", (long long)rows, (long long)cols);
+    GCB_REQUIRE(cols <= kNoAllocMaxCols && cols % 4 == 0,
+                "gcb_layernorm_bwd_noalloc_f32: cols = %lld is beyond what the fixed scratch array covers (multiples of 4 up to %d); use gcb_layernorm_bwd_f32", (long long)cols, kNoAllocMaxCols);
+    GCB_REQUIRE(aligned16(x) && aligned16(dy) && aligned16(gamma) && (dx == nullptr || aligned16(dx)), "gcb_layernorm_bwd_noalloc_f32: x, dy, gamma and dx must be 16-byte aligned");
+    float* scratch = nullptr;
+    int rc = noalloc_scratch(ctx->device, &scratch);
+    if (rc) return rc;
+    cudaSetDevice(ctx->device);
+    const bool want_params = dgamma != nullptr || dbeta != nullptr;
+    const int64_t blocks = std::min<int64_t>((rows + kNormWarps - 1) / kNormWarps, (int64_t)kNoAllocMaxBlocks);
+    const size_t smem = want_params ? sizeof(float) * kNormWarps * 2 * cols : 0;
+    const int n = pick_chunks(cols);
+    // Stage 1 overwrites the first `blocks` partial rows completely before stage 2 reads exactly those rows, so nothing
+    // left over from an earlier call can leak into this one and nothing has to be cleared.
+#define GCB_BWD(N) norm_bwd_warp<N, true><<<(unsigned)blocks, kNormWarps * 32, smem, ctx->stream>>>(dx, scratch, dy, x, gamma, mean, rstd, rows, (int)cols, acc_dx, want_params ? 1 : 0)
+    if (n == 1) GCB_BWD(1); else if (n == 2) GCB_BWD(2); else if (n == 4) GCB_BWD(4); else if (n == 6) GCB_BWD(6); else GCB_BWD(8);
+#undef GCB_BWD
+    rc = after_launch(ctx, "layernorm_bwd_noalloc");
+    if (rc) return rc;
+    if (want_params) {
+        norm_params_stage2<<<(unsigned)((2 * cols + 255) / 256), 256, 0, ctx->stream>>>(dgamma, dbeta, scratch, (int)blocks, (int)cols, acc_params);
+        rc = after_launch(ctx, "layernorm_bwd_noalloc");
+    }
+    return rc;
+}
 
 int gcb_rmsnorm_fwd_f32(gcb_ctx* ctx, float* y, float* inv_rms, const float* x, const float* gamma, int64_t rows, int64_t cols, float eps) {
     GCB_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (y && x && gamma)), "gcb_rmsnorm_fwd_f32: bad arguments");

@@ -156,6 +156,22 @@ GCB_API int gcb_layernorm_fwd_f32(gcb_ctx* ctx, float* y, float* mean /*opt*/, f
 GCB_API int gcb_layernorm_bwd_f32(gcb_ctx* ctx, float* dx /*opt*/, float* dgamma /*opt*/, float* dbeta /*opt*/, const float* dy, const float* x, const float* gamma,
                           const float* mean, const float* rstd, int64_t rows, int64_t cols, int accumulate_dx, int accumulate_dparams);
 
+/* LayerNorm backward that allocates nothing.  No counterpart in the reference.
+ * For callers that cannot take memory from an allocator while they run: code executing under a memory budget that is
+ * already fully handed out, real-time or interrupt-like host threads where an allocator lock is off limits, or hosts
+ * embedding this library next to a framework that owns every byte of device memory and forbids foreign cudaMalloc.
+ * Same arithmetic, kernels and results as gcb_layernorm_bwd_f32, but the per-CTA dgamma / dbeta partial sums live in a
+ * fixed 3.5 MiB device array that is part of the library image (every GPU that loads the library holds it until the
+ * process exits) instead of in the context's arena; the call performs no cudaMalloc, cudaFree or arena operation.
+ * Limits: cols must be a multiple of 4 and at most 1024, rows >= 1, x / dy / gamma / dx 16-byte aligned; anything else
+ * is rejected with GCB_INVALID_ARG.
+ * The first call on each device looks up the array's device address (one runtime query, no allocation); make that
+ * first call before starting any stream capture.  All calls share the one array, which keeps whatever the previous call
+ * left in it; each call overwrites the part it reads, so nothing needs clearing, but two calls that overlap on the GPU
+ * (different streams or contexts on the same device) race on it: run them one after the other. */
+GCB_API int gcb_layernorm_bwd_noalloc_f32(gcb_ctx* ctx, float* dx /*opt*/, float* dgamma /*opt*/, float* dbeta /*opt*/, const float* dy, const float* x, const float* gamma,
+                                  const float* mean, const float* rstd, int64_t rows, int64_t cols, int accumulate_dx, int accumulate_dparams);
+
 /* ---- activations: GeLUNode + BGeLU (activation_nodes.hpp:157-192, math_functors.cuh:184-214);
  *      apply_swiglu_{forward,backward}, cuda_math.hpp:51-56 ------------------------------------------ */
 GCB_API int gcb_gelu_fwd_f32(gcb_ctx* ctx, float* y, const float* x, int64_t n);
