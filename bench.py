@@ -235,7 +235,10 @@ def run_ours(args, rank, world, local_rank):
         return ms, clocks, tr.launch_count() - launches0, prof, last
 
     ms_dev, clocks, launches, prof, _ = timed(resident, True, False, True)
-    ms_e2e, _, _, _, last_loss = timed(host, False, True, False)
+    if args.no_e2e:
+        ms_e2e, last_loss = float("nan"), float("nan")
+    else:
+        ms_e2e, _, _, _, last_loss = timed(host, False, True, False)
     engine = lib.ctx_last_gemm_engine(ctx)
     tokens_per_step = B * T * accum * world
     value = tokens_per_step * K / (ms_dev / 1e3)
@@ -334,14 +337,76 @@ def run_kernels(args):
     ctx.close()
 
 
+# ---- the GEMM shapes of one gpt180m step vs the tensor roofline -------------------------------------------------------------
+def run_gemm(args):
+    import numpy as np
+    import torch
+
+    from gradcraft_b200 import capi
+
+    ctx = capi.Context(0)
+    pk = peaks()
+    M, C, F, V, T, D, BH = 32768, 1024, 4096, 32768, 1024, 64, 512
+    # name, opa, opb, M, N, K, batches (attention shapes are strided over (B, T, H*D) buffers exactly as the step runs them)
+    shapes = [
+        ("linear_fwd_NN_CxC", 0, 0, M, C, C, 1), ("linear_dX_NT_CxC", 0, 1, M, C, C, 1), ("linear_dW_TN_CxC_splitk", 1, 0, C, C, M, 1),
+        ("fc1_fwd_NN_CxF", 0, 0, M, F, C, 1), ("fc2_dW_TN_FxC", 1, 0, F, C, M, 1), ("head_fwd_NT_CxV", 0, 1, M, V, C, 1), ("head_dE_TN_VxC", 1, 0, V, C, M, 1),
+        ("attn_scores_NT_batched", 0, 1, T, T, D, BH), ("attn_pv_NN_batched", 0, 0, T, D, T, BH), ("attn_dV_TN_batched", 1, 0, T, D, T, BH),
+    ]
+    out = {}
+    for name, opa, opb, m, n, k, nb in shapes:
+        if args.only and args.only not in name:
+            continue
+        if nb == 1:
+            A = torch.randn((k, m) if opa else (m, k), device="cuda")
+            B = torch.randn((n, k) if opb else (k, n), device="cuda")
+            Cm = torch.empty(m, n, device="cuda")
+            fn = lambda: ctx.gemm_f32(opa, opb, m, n, k, 1.0, A, A.shape[1], B, B.shape[1], 0.0, Cm, n, None)
+        else:
+            Bn, H = 32, 16
+            Cw = H * D
+            q = torch.randn(Bn, T, Cw, device="cuda")
+            kk = torch.randn(Bn, T, Cw, device="cuda")
+            S = torch.randn(Bn * H, T, T, device="cuda")
+            O = torch.empty(Bn, T, Cw, device="cuda")
+            if name.startswith("attn_scores"):
+                fn = lambda: ctx.gemm_batched_f32(0, 1, T, T, D, 1.0, q, Cw, T * Cw, D, kk, Cw, T * Cw, D, 0.0, S, T, H * T * T, T * T, Bn, H)
+            elif name.startswith("attn_pv"):
+                fn = lambda: ctx.gemm_batched_f32(0, 0, T, D, T, 1.0, S, T, H * T * T, T * T, kk, Cw, T * Cw, D, 0.0, O, Cw, T * Cw, D, Bn, H)
+            else:
+                fn = lambda: ctx.gemm_batched_f32(1, 0, T, D, T, 1.0, S, T, H * T * T, T * T, q, Cw, T * Cw, D, 0.0, O, Cw, T * Cw, D, Bn, H)
+        for _ in range(max(3, args.warmup)):
+            fn()
+        ts = []
+        for _ in range(max(3, args.steps)):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        ms = float(np.median(ts))
+        fl = 2.0 * m * n * k * nb
+        out[name] = {"ms": ms, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / pk["tensor_tflops_burst"], "frac_of_3xtf32_ceiling": fl / ms / 1e9 / (pk["tensor_tflops_burst"] / 6), "engine": ctx.ctx_last_gemm_engine()}
+        del fn
+    ctx.sync()
+    worst = min(out.values(), key=lambda d: d["tflops"])
+    print(json.dumps({"metric": "GEMM engine, algorithmic TFLOP/s on the shapes of one gpt180m step", "value": worst["tflops"], "unit": "TFLOP/s (slowest shape)", "n_gpus": 1, "steps": max(3, args.steps),
+                      "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "f32 (3xTF32)", "data": "synthetic N(0,1)", "config": {"workload": "gemm", "l2": "operands of the large shapes exceed the 126 MB L2"},
+                      "peak_tflops": pk["tensor_tflops_burst"], "peak_source": pk["source"] + " dense bf16 burst", "shapes": out}))
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gpt180m", choices=list(WORKLOADS) + ["kernels"])
+    ap.add_argument("--workload", default="gpt180m", choices=list(WORKLOADS) + ["kernels", "gemm"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
+    ap.add_argument("--only", default="", help="gemm workload: run only the shapes whose name contains this text")
     args = ap.parse_args()
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
@@ -349,6 +414,9 @@ def main():
         return
     if args.workload == "kernels":
         run_kernels(args)
+        return
+    if args.workload == "gemm":
+        run_gemm(args)
         return
     run_ours(args, rank, world, local_rank)
 
