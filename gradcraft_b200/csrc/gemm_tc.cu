@@ -2,10 +2,12 @@
 // Reference counterpart: cublasSgemm / cublasSgemmStridedBatched in TF32 tensor-op mode
 // (backend/cuda/kernels_math.cu:27-36, 725-779), which keeps only 10 mantissa bits of each operand.
 //
-// One CTA computes a 128 x BN tile of C.  Warp roles:
+// Persistent CTAs (one per SM) walk over 128 x BN tiles of C.  Warp roles:
 //   warp 0      TMA producer: per 16-wide K block, one bulk tensor copy per operand tile into a 4-stage smem ring
-//   warp 1      MMA issuer: allocates BN TMEM columns, issues tcgen05.mma.kind::tf32 from shared-memory descriptors
-//   warps 2..5  splitter while the main loop runs, epilogue afterwards
+//   warp 1      MMA issuer: allocates 2 x BN TMEM columns (double-buffered accumulator), issues tcgen05.mma.kind::tf32
+//   warps 2..5  splitter: big / small parts of every landed tile
+//   warps 6..9  epilogue: TMEM -> registers -> smem transpose -> 128-byte row segments in global memory, overlapped with
+//               the main loop of the next tile
 // 3xTF32: the splitter rewrites each landed fp32 tile in place as `big` = x rounded to TF32 and writes `small` = x - big
 // (exact in fp32) to a twin tile; the issuer accumulates big*big + small*big + big*small into the same TMEM
 // accumulator, so the dropped term is small*small ~ 2^-22 of the product.
@@ -23,8 +25,8 @@
 
 namespace gcb {
 
-constexpr int TC_BM = 128, TC_BK = 16, TC_STAGES = 4;
-constexpr int TC_THREADS = 192;
+constexpr int TC_BM = 128, TC_BK = 16;
+constexpr int TC_THREADS = 320;  // producer, issuer, 4 splitter warps, 4 epilogue warps
 constexpr uint32_t kSpinLimit = 1u << 24;  // ~16M polls (each >= tens of ns): seconds, far beyond any legitimate wait
 
 struct TcParams {
@@ -36,7 +38,11 @@ struct TcParams {
     int batch_inner;
     int tiles_n, tiles_m;
     int k_blocks_per_split, k_blocks_total, splits;
-    float* partial;  // [splits][M][N] when splits > 1
+    int batches;
+    int64_t work_items;  // tiles_n * tiles_m * batches * splits
+    int split_mode;      // 1 (default): big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
+                         // 0: big = rna_tf32(x) written back, small = x - big (does not rely on the hardware's truncation)
+    float* partial;      // [splits][M][N] when splits > 1
     int* status;
 };
 
@@ -95,46 +101,69 @@ __device__ __forceinline__ float round_tf32(float x) {  // nearest TF32 value, r
     return __uint_as_float(r);
 }
 
+__device__ __forceinline__ float trunc_tf32(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+
 template <int BN>
 struct TcSmem {
+    static constexpr int STAGES = BN == 64 ? 3 : 4;  // the narrow tile keeps two CTAs per SM resident
     static constexpr int A_BYTES = TC_BM * TC_BK * 4;  // 8 KB
     static constexpr int B_BYTES = BN * TC_BK * 4;
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;  // big + small of each operand
-    static constexpr int TOTAL = TC_STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int EPI_PITCH = 36;                           // floats per staged row: 32 + 4 keeps float4 alignment and spreads banks
+    static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;       // one 32 x 32 transposition buffer per epilogue warp
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+struct TileCoord {
+    int m0, n0, b_in, b_out, split, kb0, nkb;
+};
+constexpr int TC_GROUP_M = 16;  // row tiles per raster panel: the panel's A rows and the B tiles it sweeps stay hot in L2
+__device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int64_t w, int BN) {
+    TileCoord t;
+    const int per_batch = p.tiles_n * p.tiles_m;
+    int r = (int)(w % per_batch); w /= per_batch;
+    const int batch = (int)(w % p.batches); w /= p.batches;
+    t.split = (int)w;
+    const int panel = r / (TC_GROUP_M * p.tiles_n);
+    r -= panel * TC_GROUP_M * p.tiles_n;
+    const int gm = min(TC_GROUP_M, p.tiles_m - panel * TC_GROUP_M);
+    const int tile_m = panel * TC_GROUP_M + r % gm, tile_n = r / gm;
+    t.m0 = tile_m * TC_BM; t.n0 = tile_n * BN;
+    t.b_out = batch / p.batch_inner; t.b_in = batch % p.batch_inner;
+    t.kb0 = t.split * p.k_blocks_per_split;
+    t.nkb = min(p.k_blocks_total, t.kb0 + p.k_blocks_per_split) - t.kb0;
+    return t;
+}
+
+// Persistent: CTA c processes work items c, c + gridDim.x, ... in panels of TC_GROUP_M row tiles.  The accumulator is double-buffered in TMEM (2 x BN columns): the
+// epilogue warps drain tile i while the issuer already accumulates tile i + 1.
 // A_MN: A is stored K x M (contiguous along M); B_MN: B is stored K x N (contiguous along N).
 template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
     using S = TcSmem<BN>;
+    constexpr int TC_STAGES = S::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + TC_STAGES * S::STAGE_BYTES;  // full[4], conv[4], empty[4], accum, tmem slot
+    const uint32_t bars = base + S::BAR_OFFSET;  // full[4], conv[4], empty[4], acc_full[2], acc_empty[2], tmem slot
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto conv_bar = [&](int s) { return bars + 8u * (TC_STAGES + s); };
     auto empty_bar = [&](int s) { return bars + 8u * (2 * TC_STAGES + s); };
-    const uint32_t accum_bar = bars + 8u * (3 * TC_STAGES);
-    const uint32_t tmem_slot = bars + 8u * (3 * TC_STAGES + 1);
-    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen_base + TC_STAGES * S::STAGE_BYTES + 8 * (3 * TC_STAGES + 1));
+    auto acc_full_bar = [&](int b) { return bars + 8u * (3 * TC_STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * TC_STAGES + 2 + b); };
+    const uint32_t tmem_slot = bars + 8u * (3 * TC_STAGES + 4);
+    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen_base + S::BAR_OFFSET + 8 * (3 * TC_STAGES + 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x;
-    const int tile_n = tile % p.tiles_n, tile_m = tile / p.tiles_n;
-    const int batch = blockIdx.y, split = blockIdx.z;
-    const int b_out = batch / p.batch_inner, b_in = batch % p.batch_inner;
-    const int m0 = tile_m * TC_BM, n0 = tile_n * BN;
-    const int kb0 = split * p.k_blocks_per_split;
-    const int kb1 = min(p.k_blocks_total, kb0 + p.k_blocks_per_split);
-    const int nkb = kb1 - kb0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(conv_bar(s), 4); mbar_init(empty_bar(s), 1); }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {  // TMEM allocation is warp-wide
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)(2 * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -145,24 +174,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % TC_STAGES;
-                const uint32_t ph = (uint32_t)(i / TC_STAGES) & 1u;
-                if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1)) break;
-                const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
-                mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES);
-                const int k0 = (kb0 + i) * TC_BK;
-                if (A_MN) {
+            uint32_t it = 0;  // running K-block count across tiles: stage = it % STAGES, phase = (it / STAGES) & 1
+            bool ok = true;
+            for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
+                const TileCoord tc = tile_coord(p, w, BN);
+                for (int i = 0; i < tc.nkb; ++i, ++it) {
+                    const int s = it % TC_STAGES;
+                    const uint32_t ph = (it / TC_STAGES) & 1u;
+                    ok = mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1);
+                    if (!ok) break;
+                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
+                    mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES);
+                    const int k0 = (tc.kb0 + i) * TC_BK;
+                    if (A_MN) {
 #pragma unroll
-                    for (int c = 0; c < TC_BM / 32; ++c) tma_load_4d(sa + c * 2048, &map_a, full_bar(s), m0 + 32 * c, k0, b_in, b_out);
-                } else {
-                    tma_load_4d(sa, &map_a, full_bar(s), k0, m0, b_in, b_out);
-                }
-                if (B_MN) {
+                        for (int c = 0; c < TC_BM / 32; ++c) tma_load_4d(sa + c * 2048, &map_a, full_bar(s), tc.m0 + 32 * c, k0, tc.b_in, tc.b_out);
+                    } else {
+                        tma_load_4d(sa, &map_a, full_bar(s), k0, tc.m0, tc.b_in, tc.b_out);
+                    }
+                    if (B_MN) {
 #pragma unroll
-                    for (int c = 0; c < BN / 32; ++c) tma_load_4d(sb + c * 2048, &map_b, full_bar(s), n0 + 32 * c, k0, b_in, b_out);
-                } else {
-                    tma_load_4d(sb, &map_b, full_bar(s), k0, n0, b_in, b_out);
+                        for (int c = 0; c < BN / 32; ++c) tma_load_4d(sb + c * 2048, &map_b, full_bar(s), tc.n0 + 32 * c, k0, tc.b_in, tc.b_out);
+                    } else {
+                        tma_load_4d(sb, &map_b, full_bar(s), k0, tc.n0, tc.b_in, tc.b_out);
+                    }
                 }
             }
         }
@@ -171,113 +206,147 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         if (lane == 0) {
             // instruction descriptor: fp32 accumulate, TF32 x TF32, operand majors, N >> 3, M >> 4
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            uint32_t it = 0, lt = 0;
             bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
-                const int s = i % TC_STAGES;
-                const uint32_t ph = (uint32_t)(i / TC_STAGES) & 1u;
-                ok = mbar_wait(conv_bar(s), ph, p.status, 2);
+            for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x, ++lt) {
+                const TileCoord tc = tile_coord(p, w, BN);
+                const uint32_t buf = lt & 1u;
+                ok = mbar_wait(acc_empty_bar(buf), ((lt >> 1) & 1u) ^ 1u, p.status, 5);  // the epilogue has drained this accumulator
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int i = 0; i < tc.nkb; ++i, ++it) {
+                    const int s = it % TC_STAGES;
+                    const uint32_t ph = (it / TC_STAGES) & 1u;
+                    ok = mbar_wait(p.split_mode ? full_bar(s) : conv_bar(s), ph, p.status, 2);
+                    if (ok && p.split_mode) ok = mbar_wait(conv_bar(s), ph, p.status, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
 #pragma unroll
-                for (int j = 0; j < TC_BK / 8; ++j) {
-                    const uint32_t a_off = A_MN ? j * 1024 : j * 32, b_off = B_MN ? j * 1024 : j * 32;
-                    const uint64_t a_big = A_MN ? make_desc(sa + a_off, 2048, 512, 1) : make_desc(sa + a_off, 16, 512, 4);
-                    const uint64_t a_sml = A_MN ? make_desc(sa + S::A_BYTES + a_off, 2048, 512, 1) : make_desc(sa + S::A_BYTES + a_off, 16, 512, 4);
-                    const uint64_t b_big = B_MN ? make_desc(sb + b_off, 2048, 512, 1) : make_desc(sb + b_off, 16, 512, 4);
-                    const uint64_t b_sml = B_MN ? make_desc(sb + S::B_BYTES + b_off, 2048, 512, 1) : make_desc(sb + S::B_BYTES + b_off, 16, 512, 4);
-                    umma_tf32(tmem_base, a_sml, b_big, idesc, (i | j) ? 1u : 0u);  // small terms first: they are added to a small running sum
-                    umma_tf32(tmem_base, a_big, b_sml, idesc, 1u);
-                    umma_tf32(tmem_base, a_big, b_big, idesc, 1u);
+                    for (int j = 0; j < TC_BK / 8; ++j) {
+                        const uint32_t a_off = A_MN ? j * 1024 : j * 32, b_off = B_MN ? j * 1024 : j * 32;
+                        const uint64_t a_big = A_MN ? make_desc(sa + a_off, 2048, 512, 1) : make_desc(sa + a_off, 16, 512, 4);
+                        const uint64_t a_sml = A_MN ? make_desc(sa + S::A_BYTES + a_off, 2048, 512, 1) : make_desc(sa + S::A_BYTES + a_off, 16, 512, 4);
+                        const uint64_t b_big = B_MN ? make_desc(sb + b_off, 2048, 512, 1) : make_desc(sb + b_off, 16, 512, 4);
+                        const uint64_t b_sml = B_MN ? make_desc(sb + S::B_BYTES + b_off, 2048, 512, 1) : make_desc(sb + S::B_BYTES + b_off, 16, 512, 4);
+                        umma_tf32(d_tmem, a_sml, b_big, idesc, (i | j) ? 1u : 0u);  // small terms first: they are added to a small running sum
+                        umma_tf32(d_tmem, a_big, b_sml, idesc, 1u);
+                        umma_tf32(d_tmem, a_big, b_big, idesc, 1u);
+                    }
+                    umma_commit(empty_bar(s));  // the stage may be refilled once these MMAs have read it
                 }
-                umma_commit(empty_bar(s));  // the stage may be refilled once these MMAs have read it
+                if (ok) umma_commit(acc_full_bar(buf));  // fires when every MMA of this tile has completed
             }
-            umma_commit(accum_bar);  // fires when every MMA issued so far has completed
         }
-    } else {
-        // ---------------- splitter, then epilogue ----------------
+    } else if (warp < 6) {
+        // ---------------- splitter ----------------
         const int t = threadIdx.x - 64;  // 0..127
+        uint32_t it = 0;
         bool ok = true;
-        for (int i = 0; i < nkb && ok; ++i) {
-            const int s = i % TC_STAGES;
-            const uint32_t ph = (uint32_t)(i / TC_STAGES) & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, 3)) != 0;
-            if (!ok) break;
-            float4* stage = reinterpret_cast<float4*>(gen_base + s * S::STAGE_BYTES);
-            // the twin tile sits one tile size after its source, same (swizzled) position inside the tile
-            auto split_tile = [&](float4* big, int n_vec, int twin_vec) {
+        for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
+            const TileCoord tc = tile_coord(p, w, BN);
+            for (int i = 0; i < tc.nkb; ++i, ++it) {
+                const int s = it % TC_STAGES;
+                const uint32_t ph = (it / TC_STAGES) & 1u;
+                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, 3)) != 0;
+                if (!ok) break;
+                float4* stage = reinterpret_cast<float4*>(gen_base + s * S::STAGE_BYTES);
+                // the twin tile sits one tile size after its source, same (swizzled) position inside the tile
+                auto split_tile = [&](float4* big, int n_vec, int twin_vec) {
+                    if (p.split_mode) {  // the tensor core drops the 13 low mantissa bits itself: big stays as loaded
 #pragma unroll
-                for (int q = 0; q < n_vec / 128; ++q) {
-                    const float4 x = big[t + 128 * q];
-                    const float4 b = make_float4(round_tf32(x.x), round_tf32(x.y), round_tf32(x.z), round_tf32(x.w));
-                    const float4 sm = make_float4(x.x - b.x, x.y - b.y, x.z - b.z, x.w - b.w);
-                    big[t + 128 * q] = b;
-                    big[t + 128 * q + twin_vec] = sm;
-                }
-            };
-            split_tile(stage, S::A_BYTES / 16, S::A_BYTES / 16);
-            split_tile(stage + 2 * (S::A_BYTES / 16), S::B_BYTES / 16, S::B_BYTES / 16);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core's reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(conv_bar(s));
-        }
-        // epilogue: warp w owns TMEM lanes 32 * (w % 4) .. +31, i.e. 32 rows of the tile
-        if (ok && nkb > 0) ok = mbar_wait(accum_bar, 0, p.status, 4);
-        ok = __all_sync(0xffffffffu, ok) != 0;  // the TMEM loads below are warp-wide: take one decision per warp
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int q = warp & 3;
-        const int64_t m = (int64_t)m0 + 32 * q + lane;
-        if (ok) {
-            const bool to_partial = p.splits > 1;
-            float* crow = to_partial ? p.partial + ((int64_t)split * p.M + m) * p.N : p.C + (int64_t)b_out * p.c_so + (int64_t)b_in * p.c_si + m * p.ldc;
-            const bool vec_ok = to_partial ? (p.N % 4 == 0) : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
-            const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                float v[32];
-                if (nkb > 0) tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), v);
-                else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) v[e] = 0.0f;
-                }
-                const int64_t nb = (int64_t)n0 + 32 * c;
-                if (m < p.M && nb < p.N) {
-                    if (to_partial) {
-#pragma unroll
-                        for (int e = 0; e < 32; e += 4) {
-                            if (vec_ok && nb + e + 3 < p.N) st4(crow + nb + e, make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]));
-                            else for (int u = 0; u < 4; ++u) if (nb + e + u < p.N) crow[nb + e + u] = v[e + u];
+                        for (int q = 0; q < n_vec / 128; ++q) {
+                            const float4 x = big[t + 128 * q];
+                            big[t + 128 * q + twin_vec] = make_float4(round_tf32(x.x - trunc_tf32(x.x)), round_tf32(x.y - trunc_tf32(x.y)), round_tf32(x.z - trunc_tf32(x.z)), round_tf32(x.w - trunc_tf32(x.w)));
                         }
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 32; e += 4) {
-                            if (vec_ok && nb + e + 3 < p.N) {
-                                float4 o = make_float4(p.alpha * v[e], p.alpha * v[e + 1], p.alpha * v[e + 2], p.alpha * v[e + 3]);
-                                if (p.bias) { const float4 bb = bias_vec ? __ldg(reinterpret_cast<const float4*>(p.bias + nb + e)) : make_float4(p.bias[nb + e], p.bias[nb + e + 1], p.bias[nb + e + 2], p.bias[nb + e + 3]); o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w; }
-                                if (p.beta != 0.0f) { const float4 old = ld4(crow + nb + e); o.x += p.beta * old.x; o.y += p.beta * old.y; o.z += p.beta * old.z; o.w += p.beta * old.w; }
-                                st4(crow + nb + e, o);
-                            } else {
-                                for (int u = 0; u < 4; ++u) {
-                                    const int64_t n = nb + e + u;
-                                    if (n < p.N) {
-                                        float o = p.alpha * v[e + u];
-                                        if (p.bias) o += p.bias[n];
-                                        if (p.beta != 0.0f) o += p.beta * crow[n];
-                                        crow[n] = o;
-                                    }
+                        for (int q = 0; q < n_vec / 128; ++q) {
+                            const float4 x = big[t + 128 * q];
+                            const float4 b = make_float4(round_tf32(x.x), round_tf32(x.y), round_tf32(x.z), round_tf32(x.w));
+                            big[t + 128 * q] = b;
+                            big[t + 128 * q + twin_vec] = make_float4(x.x - b.x, x.y - b.y, x.z - b.z, x.w - b.w);
+                        }
+                    }
+                };
+                split_tile(stage, S::A_BYTES / 16, S::A_BYTES / 16);
+                split_tile(stage + 2 * (S::A_BYTES / 16), S::B_BYTES / 16, S::B_BYTES / 16);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(conv_bar(s));
+            }
+        }
+    } else {
+        // ---------------- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. +31, i.e. 32 rows of the tile ----------------
+        const int q = warp & 3;
+        float* stg = reinterpret_cast<float*>(gen_base + TC_STAGES * S::STAGE_BYTES) + q * 32 * S::EPI_PITCH;
+        const bool to_partial = p.splits > 1;
+        const bool vec_ok = to_partial ? (p.N % 4 == 0) : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
+        const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
+        const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;  // store phase: 4 rows x 8 float4 per instruction (128 B per row)
+        uint32_t lt = 0;
+        bool ok = true;
+        for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x, ++lt) {
+            const TileCoord tc = tile_coord(p, w, BN);
+            const uint32_t buf = lt & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float* cbase = to_partial ? p.partial + (int64_t)tc.split * p.M * p.N : p.C + (int64_t)tc.b_out * p.c_so + (int64_t)tc.b_in * p.c_si;
+            const int64_t ld = to_partial ? p.N : p.ldc;
+            const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
+            const float* bias = to_partial ? nullptr : p.bias;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int64_t nb = (int64_t)tc.n0 + 32 * c;
+                if (nb >= p.N) break;  // warp-uniform
+                float v[32];
+                tmem_ld32(tmem_base + buf * BN + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), v);
+                // transpose through shared memory so that a warp stores whole 128-byte row segments
+#pragma unroll
+                for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(stg + lane * S::EPI_PITCH + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                __syncwarp();
+#pragma unroll
+                for (int r4 = 0; r4 < 8; ++r4) {
+                    const int row = r4 * 4 + sub_r;
+                    const int64_t m = (int64_t)tc.m0 + 32 * q + row, n = nb + sub_c;
+                    if (m < p.M && n < p.N) {
+                        float4 o = *reinterpret_cast<const float4*>(stg + row * S::EPI_PITCH + sub_c);
+                        o.x *= alpha; o.y *= alpha; o.z *= alpha; o.w *= alpha;
+                        float* dst = cbase + m * ld + n;
+                        if (vec_ok && n + 3 < p.N) {
+                            if (bias) {
+                                const float4 bb = bias_vec ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(bias[n], bias[n + 1], bias[n + 2], bias[n + 3]);
+                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                            }
+                            if (beta != 0.0f) { const float4 old = ld4(dst); o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w; }
+                            st4(dst, o);
+                        } else {
+                            const float ov[4] = {o.x, o.y, o.z, o.w};
+                            for (int u = 0; u < 4; ++u) {
+                                if (n + u < p.N) {
+                                    float r = ov[u];
+                                    if (bias) r += bias[n + u];
+                                    if (beta != 0.0f) r += beta * dst[u];
+                                    dst[u] = r;
                                 }
                             }
                         }
                     }
                 }
+                __syncwarp();
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(buf));  // this accumulator may be overwritten
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
     }
 }
 
@@ -381,11 +450,18 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     p.status = ctx->d_status;
     const int64_t tiles = (int64_t)p.tiles_n * p.tiles_m * batches;
     if (tiles > 2147483647LL / 2) return GCB_UNSUPPORTED;
-    // split-K when the tiles alone would leave most of the 148 SMs idle
+    // split-K when the tiles alone would leave SMs idle: pick the slice count with the lowest modelled time
+    // (rounds of 148 persistent CTAs x K blocks per slice, plus writing and re-reading the partial tiles)
     int splits = 1;
-    if (batches == 1 && tiles < kSMs && p.k_blocks_total >= 64) {
-        splits = (int)std::min<int64_t>((2 * kSMs + tiles - 1) / tiles, p.k_blocks_total / 32);
-        splits = std::max(1, std::min(splits, 32));
+    if (batches == 1 && p.k_blocks_total >= 64) {
+        const int ctas = kSMs * (BN == 64 ? 2 : 1);
+        double best = 1e30;
+        for (int sp = 1; sp <= 32 && p.k_blocks_total / sp >= 16; ++sp) {
+            const int kbs = (p.k_blocks_total + sp - 1) / sp;
+            const int64_t rounds = (tiles * sp + ctas - 1) / ctas;
+            const double t_us = (double)rounds * (kbs * 0.5 + 2.0) + (sp > 1 ? (double)sp * g.M * g.N * 8.0 / 5.0e6 : 0.0);
+            if (t_us < best * 0.97) { best = t_us; splits = sp; }
+        }
     }
     p.splits = splits;
     p.k_blocks_per_split = (p.k_blocks_total + splits - 1) / splits;
@@ -397,7 +473,11 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
         if (rc) return rc;
         p.partial = sc.as<float>();
     }
-    dim3 grid((unsigned)(p.tiles_n * p.tiles_m), (unsigned)batches, (unsigned)splits);
+    p.batches = (int)batches;
+    p.work_items = (int64_t)p.tiles_n * p.tiles_m * batches * splits;
+    static const int split_mode_env = [] { const char* e = getenv("GRADC_TC_SPLIT_MODE"); return e ? atoi(e) : 1; }();
+    p.split_mode = split_mode_env;
+    dim3 grid((unsigned)std::min<int64_t>(p.work_items, (int64_t)kSMs * (BN == 64 ? 2 : 1)), 1, 1);
     int rc;
     if (BN == 256) rc = launch_bn<256>(ctx, ta, tb, ma, mb, p, grid);
     else if (BN == 128) rc = launch_bn<128>(ctx, ta, tb, ma, mb, p, grid);

@@ -147,6 +147,131 @@ __global__ void __launch_bounds__(kNormWarps * 32) norm_bwd_warp(float* __restri
     }
 }
 
+// ---- backward, staged: rows stream through a per-warp shared-memory ring filled by bulk async copies -------------
+// The register version above keeps x and dy of a row in registers (64 per lane at 1024 columns) next to the running
+// dgamma / dbeta sums, which leaves 8 warps per SM and too few bytes in flight.  Here lane 0 of every warp keeps kRing
+// rows (x and dy, 8 KB each at 1024 columns) in flight with cp.async.bulk + mbarrier, the warp reads a landed row from
+// shared memory twice (statistics, then dx), and only the column sums stay in registers: 8 warps x 3 rows x 8 KB = 192 KB
+// in flight per SM, independent of register pressure.  Waits are bounded and report through the status word.
+constexpr int kRing = 3, kRingWarps = 8;
+__device__ __forceinline__ uint32_t nsm_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, int* status) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (i > 4096) __nanosleep(32);
+    }
+    atomicExch(&status[0], 1);
+    atomicExch(&status[1], 100);
+    return false;
+}
+__device__ __forceinline__ void ring_fetch(uint32_t bar, uint32_t dst, const float* x_row, const float* dy_row, uint32_t row_bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2u * row_bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(x_row), "r"(row_bytes), "r"(bar) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + row_bytes), "l"(dy_row), "r"(row_bytes), "r"(bar) : "memory");
+}
+
+template <int NCHUNK, bool IS_LN>
+__global__ void __launch_bounds__(kRingWarps * 32, 1) norm_bwd_ring(float* __restrict__ dx, float* __restrict__ partial, const float* __restrict__ dy, const float* __restrict__ x,
+                                                                    const float* __restrict__ gamma, const float* __restrict__ stat0, const float* __restrict__ stat1, int64_t rows, int cols,
+                                                                    int acc_dx, int want_params, int* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t ring_smem[];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint32_t row_bytes = (uint32_t)cols * 4u;
+    // layout: [warp][stage][x row | dy row], then gamma, then one mbarrier per (warp, stage)
+    float* my_ring = reinterpret_cast<float*>(ring_smem) + (size_t)wid * kRing * 2 * cols;
+    float* sgamma = reinterpret_cast<float*>(ring_smem) + (size_t)kRingWarps * kRing * 2 * cols;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sgamma + cols);
+    const uint32_t my_bar0 = nsm_u32(bars + wid * kRing);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) sgamma[c] = gamma[c];
+    if (lane == 0) {
+        for (int s = 0; s < kRing; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(my_bar0 + 8u * s));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int64_t warp = (int64_t)blockIdx.x * kRingWarps + wid, nwarps = (int64_t)gridDim.x * kRingWarps;
+    const float inv_c = 1.0f / (float)cols;
+    float4 dg[NCHUNK], db[NCHUNK];
+#pragma unroll
+    for (int k = 0; k < NCHUNK; ++k) { dg[k] = make_float4(0.f, 0.f, 0.f, 0.f); db[k] = dg[k]; }
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kRing; ++s) {
+            const int64_t r = warp + (int64_t)s * nwarps;
+            if (r < rows) ring_fetch(my_bar0 + 8u * s, nsm_u32(my_ring + (size_t)s * 2 * cols), x + r * cols, dy + r * cols, row_bytes);
+        }
+    }
+    uint32_t n = 0;
+    // the row statistics are fetched one row ahead so that their global-memory latency is off the per-row critical path
+    float mu_next = (IS_LN && warp < rows) ? stat0[warp] : 0.0f;
+    float rs_next = warp < rows ? (IS_LN ? stat1[warp] : stat0[warp]) : 0.0f;
+    for (int64_t r = warp; r < rows; r += nwarps, ++n) {
+        const int s = n % kRing;
+        const uint32_t parity = (n / kRing) & 1u;
+        const float mu = mu_next, rs = rs_next;
+        if (r + nwarps < rows) {
+            mu_next = IS_LN ? stat0[r + nwarps] : 0.0f;
+            rs_next = IS_LN ? stat1[r + nwarps] : stat0[r + nwarps];
+        }
+        if (!__all_sync(0xffffffffu, ring_wait(my_bar0 + 8u * s, parity, status))) break;
+        const float* xs = my_ring + (size_t)s * 2 * cols;
+        const float* ds = xs + cols;
+        float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < NCHUNK; ++k) {
+            const int c = (lane + 32 * k) * 4;
+            if (c < cols) {
+                const float4 xv = ld4(xs + c), dv = ld4(ds + c), g = ld4(sgamma + c);
+                const float4 xh = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
+                dg[k].x += dv.x * xh.x; dg[k].y += dv.y * xh.y; dg[k].z += dv.z * xh.z; dg[k].w += dv.w * xh.w;
+                if (IS_LN) { db[k].x += dv.x; db[k].y += dv.y; db[k].z += dv.z; db[k].w += dv.w; }
+                const float4 gg = make_float4(dv.x * g.x, dv.y * g.y, dv.z * g.z, dv.w * g.w);
+                if (IS_LN) s1 += gg.x + gg.y + gg.z + gg.w;
+                s2 += gg.x * xh.x + gg.y * xh.y + gg.z * xh.z + gg.w * xh.w;
+            }
+        }
+        if (dx != nullptr) {
+            if (IS_LN) s1 = warp_sum(s1);
+            s2 = warp_sum(s2);
+            const float m1 = s1 * inv_c, m2 = s2 * inv_c;
+            float* or_ = dx + r * cols;
+#pragma unroll
+            for (int k = 0; k < NCHUNK; ++k) {
+                const int c = (lane + 32 * k) * 4;
+                if (c < cols) {
+                    const float4 xv = ld4(xs + c), dv = ld4(ds + c), g = ld4(sgamma + c);
+                    float4 o = make_float4(rs * (dv.x * g.x - m1 - (xv.x - mu) * rs * m2), rs * (dv.y * g.y - m1 - (xv.y - mu) * rs * m2), rs * (dv.z * g.z - m1 - (xv.z - mu) * rs * m2),
+                                           rs * (dv.w * g.w - m1 - (xv.w - mu) * rs * m2));
+                    if (acc_dx) { const float4 old = ld4(or_ + c); o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+                    st4_stream(or_ + c, o);
+                }
+            }
+        }
+        __syncwarp();  // every lane is done reading this stage before it is refilled
+        const int64_t nr = r + (int64_t)kRing * nwarps;
+        if (lane == 0 && nr < rows) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (lane == 0 && nr < rows) ring_fetch(my_bar0 + 8u * s, nsm_u32(my_ring + (size_t)s * 2 * cols), x + nr * cols, dy + nr * cols, row_bytes);
+    }
+    if (!want_params) return;
+    __syncthreads();  // all rings are idle: reuse them for the cross-warp sum of the column totals
+    float* red = reinterpret_cast<float*>(ring_smem);
+    float* mine = red + (size_t)wid * 2 * cols;
+#pragma unroll
+    for (int k = 0; k < NCHUNK; ++k) {
+        const int c = (lane + 32 * k) * 4;
+        if (c < cols) { st4(mine + c, dg[k]); st4(mine + cols + c, db[k]); }
+    }
+    __syncthreads();
+    float* outp = partial + (size_t)blockIdx.x * 2 * cols;
+    for (int i = threadIdx.x; i < 2 * cols; i += kRingWarps * 32) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kRingWarps; ++w) s += red[(size_t)w * 2 * cols + i];
+        outp[i] = s;
+    }
+}
+
 __global__ void __launch_bounds__(256) norm_params_stage2(float* __restrict__ dgamma, float* __restrict__ dbeta, const float* __restrict__ partial, int nparts, int cols, int accumulate) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;  // over 2 * cols
     if (i >= 2 * cols) return;
@@ -277,6 +402,30 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
     }
     const bool fast = cols % 4 == 0 && cols <= 1024 && aligned16(x) && aligned16(dy) && aligned16(gamma) && (dx == nullptr || aligned16(dx));
     const char* name = IS_LN ? "layernorm_bwd" : "rmsnorm_bwd";
+    if (fast && rows >= 4 * kSMs * kRingWarps && (dx == nullptr || aligned16(dx))) {
+        // large inputs: one persistent CTA per SM, rows staged through shared memory by bulk async copies
+        const int64_t blocks = kSMs;
+        Scratch sc(ctx);
+        if (want_params) { int rc = sc.get(sizeof(float) * blocks * 2 * cols); if (rc) return rc; }
+        const size_t smem = sizeof(float) * ((size_t)kRingWarps * kRing * 2 * cols + cols) + sizeof(uint64_t) * kRingWarps * kRing;
+        const int n = pick_chunks(cols);
+#define GCB_RING(N)                                                                                                                                      \
+        do {                                                                                                                                             \
+            auto kfn = norm_bwd_ring<N, IS_LN>;                                                                                                          \
+            static bool attr_done = false;                                                                                                               \
+            if (!attr_done) { GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_done = true; }     \
+            kfn<<<(unsigned)blocks, kRingWarps * 32, smem, ctx->stream>>>(dx, sc.as<float>(), dy, x, gamma, s0, s1, rows, (int)cols, acc_dx, want_params ? 1 : 0, ctx->d_status); \
+        } while (0)
+        if (n == 1) GCB_RING(1); else if (n == 2) GCB_RING(2); else if (n == 4) GCB_RING(4); else if (n == 6) GCB_RING(6); else GCB_RING(8);
+#undef GCB_RING
+        int rc = after_launch(ctx, name);
+        if (rc) return rc;
+        if (want_params) {
+            norm_params_stage2<<<(unsigned)((2 * cols + 255) / 256), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params);
+            rc = after_launch(ctx, name);
+        }
+        return rc;
+    }
     if (fast) {
         // 3 CTAs of 4 warps per SM: ~170 registers per thread, 96 KB of row data in flight per SM
         int64_t blocks = std::min<int64_t>((rows + kNormWarps - 1) / kNormWarps, (int64_t)kSMs * 3);

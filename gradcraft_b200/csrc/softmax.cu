@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) causal_softmax_fwd_warp(float* 
 }
 
 template <int NCHUNK>
-__global__ void __launch_bounds__(kSmWarps * 32) causal_softmax_bwd_warp(float* __restrict__ ds, const float* __restrict__ dp, const float* __restrict__ probs, float scale,
+__global__ void __launch_bounds__(kSmWarps * 32, (NCHUNK == 8 ? 3 : 4)) causal_softmax_bwd_warp(float* __restrict__ ds, const float* __restrict__ dp, const float* __restrict__ probs, float scale,
                                                                          int64_t rows, int T, int accumulate) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * kSmWarps + (threadIdx.x >> 5);
