@@ -347,7 +347,8 @@ def run_gemm(args):
     ctx = capi.Context(0)
     pk = peaks()
     M, C, F, V, T, D, BH = 32768, 1024, 4096, 32768, 1024, 64, 512
-    # name, opa, opb, M, N, K, batches (attention shapes are strided over (B, T, H*D) buffers exactly as the step runs them)
+    # name, opa, opb, M, N, K, batches (attention shapes are strided over (B, T, H*D) buffers exactly as the step runs them: causal
+    # variants that skip known zeros; their TFLOP/s are quoted on the dense 2*M*N*K count, as the reference computes them)
     shapes = [
         ("linear_fwd_NN_CxC", 0, 0, M, C, C, 1), ("linear_dX_NT_CxC", 0, 1, M, C, C, 1), ("linear_dW_TN_CxC_splitk", 1, 0, C, C, M, 1),
         ("fc1_fwd_NN_CxF", 0, 0, M, F, C, 1), ("fc2_dW_TN_FxC", 1, 0, F, C, M, 1), ("head_fwd_NT_CxV", 0, 1, M, V, C, 1), ("head_dE_TN_VxC", 1, 0, V, C, M, 1),
@@ -370,11 +371,11 @@ def run_gemm(args):
             S = torch.randn(Bn * H, T, T, device="cuda")
             O = torch.empty(Bn, T, Cw, device="cuda")
             if name.startswith("attn_scores"):
-                fn = lambda: ctx.gemm_batched_f32(0, 1, T, T, D, 1.0, q, Cw, T * Cw, D, kk, Cw, T * Cw, D, 0.0, S, T, H * T * T, T * T, Bn, H)
+                fn = lambda: ctx.gemm_batched_causal_f32(0, 1, T, T, D, 1.0, q, Cw, T * Cw, D, kk, Cw, T * Cw, D, 0.0, S, T, H * T * T, T * T, Bn, H, 1)
             elif name.startswith("attn_pv"):
-                fn = lambda: ctx.gemm_batched_f32(0, 0, T, D, T, 1.0, S, T, H * T * T, T * T, kk, Cw, T * Cw, D, 0.0, O, Cw, T * Cw, D, Bn, H)
+                fn = lambda: ctx.gemm_batched_causal_f32(0, 0, T, D, T, 1.0, S, T, H * T * T, T * T, kk, Cw, T * Cw, D, 0.0, O, Cw, T * Cw, D, Bn, H, 2)
             else:
-                fn = lambda: ctx.gemm_batched_f32(1, 0, T, D, T, 1.0, S, T, H * T * T, T * T, q, Cw, T * Cw, D, 0.0, O, Cw, T * Cw, D, Bn, H)
+                fn = lambda: ctx.gemm_batched_causal_f32(1, 0, T, D, T, 1.0, S, T, H * T * T, T * T, q, Cw, T * Cw, D, 0.0, O, Cw, T * Cw, D, Bn, H, 3)
         for _ in range(max(3, args.warmup)):
             fn()
         ts = []

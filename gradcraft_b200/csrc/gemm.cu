@@ -53,6 +53,18 @@ int gcb_gemm_batched_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N,
     return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_batched_f32");
 }
 
+int gcb_gemm_batched_causal_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda, int64_t a_so, int64_t a_si, const float* B,
+                                int64_t ldb, int64_t b_so, int64_t b_si, float beta, float* C, int64_t ldc, int64_t c_so, int64_t c_si, int64_t batch_outer, int64_t batch_inner, int causal) {
+    GCB_REQUIRE(ctx, "gcb_gemm_batched_causal_f32: ctx is NULL");
+    GCB_REQUIRE(batch_outer >= 0 && batch_inner >= 0, "gcb_gemm_batched_causal_f32: negative batch count");
+    GCB_REQUIRE(causal >= 0 && causal <= 3, "gcb_gemm_batched_causal_f32: causal must be 0..3");
+    GCB_REQUIRE(causal != 1 || M == N, "gcb_gemm_batched_causal_f32: a triangular output needs M == N");
+    GCB_REQUIRE(causal < 2 || M == K, "gcb_gemm_batched_causal_f32: a triangular op(A) needs M == K");
+    GemmArgs g{M, N, K, alpha, beta, A, B, nullptr, C, lda, ldb, ldc, a_so, a_si, b_so, b_si, c_so, c_si, batch_outer, batch_inner};
+    g.causal = causal;
+    return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_batched_causal_f32");
+}
+
 int gcb_profile_gemm_begin(gcb_ctx* ctx) {
     GCB_REQUIRE(ctx, "gcb_profile_gemm_begin: ctx is NULL");
     ctx->prof_on = true;

@@ -12,6 +12,7 @@ struct GemmArgs {
     int64_t lda, ldb, ldc;
     int64_t a_so, a_si, b_so, b_si, c_so, c_si;  // batch strides (outer, inner) in elements
     int64_t batch_outer, batch_inner;
+    int causal = 0;  // 0 none; 1 output needed on/below the diagonal only; 2 op(A)[m,k] = 0 for k > m; 3 op(A)[m,k] = 0 for k < m
 };
 
 // fp32 FMA engine: any shape, any leading dimension.

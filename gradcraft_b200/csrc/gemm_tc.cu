@@ -40,6 +40,7 @@ struct TcParams {
     int k_blocks_per_split, k_blocks_total, splits;
     int batches;
     int64_t work_items;  // tiles_n * tiles_m * batches * splits
+    int causal;          // see GemmArgs::causal
     int split_mode;      // 1 (default): big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
                          // 0: big = rna_tf32(x) written back, small = x - big (does not rely on the hardware's truncation)
     float* partial;      // [splits][M][N] when splits > 1
@@ -117,6 +118,7 @@ struct TcSmem {
 
 struct TileCoord {
     int m0, n0, b_in, b_out, split, kb0, nkb;
+    bool skip;
 };
 constexpr int TC_GROUP_M = 16;  // row tiles per raster panel: the panel's A rows and the B tiles it sweeps stay hot in L2
 __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int64_t w, int BN) {
@@ -132,7 +134,12 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int64_t w, in
     t.m0 = tile_m * TC_BM; t.n0 = tile_n * BN;
     t.b_out = batch / p.batch_inner; t.b_in = batch % p.batch_inner;
     t.kb0 = t.split * p.k_blocks_per_split;
-    t.nkb = min(p.k_blocks_total, t.kb0 + p.k_blocks_per_split) - t.kb0;
+    int kb1 = min(p.k_blocks_total, t.kb0 + p.k_blocks_per_split);
+    t.skip = false;
+    if (p.causal == 1) t.skip = t.n0 >= t.m0 + TC_BM;                                   // tile entirely above the diagonal
+    else if (p.causal == 2) kb1 = min(kb1, (t.m0 + TC_BM + TC_BK - 1) / TC_BK);           // op(A) is zero right of the diagonal
+    else if (p.causal == 3) t.kb0 = max(t.kb0, t.m0 / TC_BK);                             // op(A) is zero left of the diagonal
+    t.nkb = kb1 - t.kb0;
     return t;
 }
 
@@ -178,6 +185,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
             bool ok = true;
             for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
                 const TileCoord tc = tile_coord(p, w, BN);
+                if (tc.skip) continue;
                 for (int i = 0; i < tc.nkb; ++i, ++it) {
                     const int s = it % TC_STAGES;
                     const uint32_t ph = (it / TC_STAGES) & 1u;
@@ -208,8 +216,9 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
             uint32_t it = 0, lt = 0;
             bool ok = true;
-            for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x, ++lt) {
+            for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
                 const TileCoord tc = tile_coord(p, w, BN);
+                if (tc.skip) continue;
                 const uint32_t buf = lt & 1u;
                 ok = mbar_wait(acc_empty_bar(buf), ((lt >> 1) & 1u) ^ 1u, p.status, 5);  // the epilogue has drained this accumulator
                 if (!ok) break;
@@ -237,6 +246,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                     umma_commit(empty_bar(s));  // the stage may be refilled once these MMAs have read it
                 }
                 if (ok) umma_commit(acc_full_bar(buf));  // fires when every MMA of this tile has completed
+                ++lt;
             }
         }
     } else if (warp < 6) {
@@ -246,6 +256,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
         bool ok = true;
         for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
             const TileCoord tc = tile_coord(p, w, BN);
+            if (tc.skip) continue;
             for (int i = 0; i < tc.nkb; ++i, ++it) {
                 const int s = it % TC_STAGES;
                 const uint32_t ph = (it / TC_STAGES) & 1u;
@@ -287,8 +298,9 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
         const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;  // store phase: 4 rows x 8 float4 per instruction (128 B per row)
         uint32_t lt = 0;
         bool ok = true;
-        for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x, ++lt) {
+        for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
             const TileCoord tc = tile_coord(p, w, BN);
+            if (tc.skip) continue;
             const uint32_t buf = lt & 1u;
             ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0;
             if (!ok) break;
@@ -340,6 +352,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(buf));  // this accumulator may be overwritten
+            ++lt;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -474,6 +487,7 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
         p.partial = sc.as<float>();
     }
     p.batches = (int)batches;
+    p.causal = g.causal;
     p.work_items = (int64_t)p.tiles_n * p.tiles_m * batches * splits;
     static const int split_mode_env = [] { const char* e = getenv("GRADC_TC_SPLIT_MODE"); return e ? atoi(e) : 1; }();
     p.split_mode = split_mode_env;

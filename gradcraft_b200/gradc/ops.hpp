@@ -599,6 +599,8 @@ inline Tensor<float> matmul(Tensor<float> x, Tensor<float> w) { return linear(st
 
 // ---- attention ----------------------------------------------------------------------------------------------------
 // softmax_causal(q k^T / sqrt(D)) v on (B, H, T, D) operands of any batch/row strides (frontend/tensor_other.hpp:53-93).
+// The six batched GEMMs skip what causality zeroes: score / dP tiles above the diagonal are not computed, and the K loops
+// over the (transposed) probability matrices stop / start at the diagonal.
 // q, k, v are read in place through two-level batch strides — the head split reshape+permute of the attention layer
 // stays a view — and the output is laid out (B, T, H, D) in memory, so merging heads is a view as well.
 class SDPANode : public Node<float> {
@@ -621,10 +623,10 @@ public:
         m_probs = Tensor<float>({B * H, T, T}, m_q.device(), uninitialized);
         int64_t qo, qi, ql, ko, ki, kl, vo, vi, vl;
         strides4(m_q, qo, qi, ql); strides4(m_k, ko, ki, kl); strides4(m_v, vo, vi, vl);
-        gcb_check(gcb_gemm_batched_f32(c, GCB_OP_N, GCB_OP_T, T, T, D, 1.0f, m_q.data_ptr(), ql, qo, qi, m_k.data_ptr(), kl, ko, ki, 0.0f, m_probs.data_ptr(), T, H * T * T, T * T, B, H), "attention scores");
+        gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_T, T, T, D, 1.0f, m_q.data_ptr(), ql, qo, qi, m_k.data_ptr(), kl, ko, ki, 0.0f, m_probs.data_ptr(), T, H * T * T, T * T, B, H, 1), "attention scores");
         gcb_check(gcb_causal_softmax_fwd_f32(c, m_probs.data_ptr(), m_probs.data_ptr(), m_scale, B * H * T, T), "causal softmax");
         Tensor<float> mem({B, T, H, D}, m_q.device(), uninitialized);
-        gcb_check(gcb_gemm_batched_f32(c, GCB_OP_N, GCB_OP_N, T, D, T, 1.0f, m_probs.data_ptr(), T, H * T * T, T * T, m_v.data_ptr(), vl, vo, vi, 0.0f, mem.data_ptr(), H * D, T * H * D, D, B, H), "attention output");
+        gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_N, T, D, T, 1.0f, m_probs.data_ptr(), T, H * T * T, T * T, m_v.data_ptr(), vl, vo, vi, 0.0f, mem.data_ptr(), H * D, T * H * D, D, B, H, 2), "attention output");
         return Tensor<float>({B, H, T, D}, out_strides(H, T, D), 0, mem._get_storage(), false);
     }
     void backward(const Tensor<float>& g_in, bool retain_graph) override {
@@ -640,21 +642,21 @@ public:
         };
         if (m_v.requires_grad()) {  // dV = P^T . dO
             Tensor<float> dv = fresh();
-            gcb_check(gcb_gemm_batched_f32(c, GCB_OP_T, GCB_OP_N, T, D, T, 1.0f, m_probs.data_ptr(), T, H * T * T, T * T, g.data_ptr(), gl, go, gi, 0.0f, dv.data_ptr(), H * D, T * H * D, D, B, H), "attention dV");
+            gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_T, GCB_OP_N, T, D, T, 1.0f, m_probs.data_ptr(), T, H * T * T, T * T, g.data_ptr(), gl, go, gi, 0.0f, dv.data_ptr(), H * D, T * H * D, D, B, H, 3), "attention dV");
             push_grad(m_v, dv);
         }
         if (m_q.requires_grad() || m_k.requires_grad()) {
             Tensor<float> ds({B * H, T, T}, g.device(), uninitialized);  // dP = dO . V^T, then dS in place
-            gcb_check(gcb_gemm_batched_f32(c, GCB_OP_N, GCB_OP_T, T, T, D, 1.0f, g.data_ptr(), gl, go, gi, m_v.data_ptr(), vl, vo, vi, 0.0f, ds.data_ptr(), T, H * T * T, T * T, B, H), "attention dP");
+            gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_T, T, T, D, 1.0f, g.data_ptr(), gl, go, gi, m_v.data_ptr(), vl, vo, vi, 0.0f, ds.data_ptr(), T, H * T * T, T * T, B, H, 1), "attention dP");
             gcb_check(gcb_causal_softmax_bwd_f32(c, ds.data_ptr(), ds.data_ptr(), m_probs.data_ptr(), m_scale, B * H * T, T, 0), "causal softmax backward");
             if (m_q.requires_grad()) {  // dQ = dS . K
                 Tensor<float> dq = fresh();
-                gcb_check(gcb_gemm_batched_f32(c, GCB_OP_N, GCB_OP_N, T, D, T, 1.0f, ds.data_ptr(), T, H * T * T, T * T, m_k.data_ptr(), kl, ko, ki, 0.0f, dq.data_ptr(), H * D, T * H * D, D, B, H), "attention dQ");
+                gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_N, T, D, T, 1.0f, ds.data_ptr(), T, H * T * T, T * T, m_k.data_ptr(), kl, ko, ki, 0.0f, dq.data_ptr(), H * D, T * H * D, D, B, H, 2), "attention dQ");
                 push_grad(m_q, dq);
             }
             if (m_k.requires_grad()) {  // dK = dS^T . Q
                 Tensor<float> dk = fresh();
-                gcb_check(gcb_gemm_batched_f32(c, GCB_OP_T, GCB_OP_N, T, D, T, 1.0f, ds.data_ptr(), T, H * T * T, T * T, m_q.data_ptr(), ql, qo, qi, 0.0f, dk.data_ptr(), H * D, T * H * D, D, B, H), "attention dK");
+                gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_T, GCB_OP_N, T, D, T, 1.0f, ds.data_ptr(), T, H * T * T, T * T, m_q.data_ptr(), ql, qo, qi, 0.0f, dk.data_ptr(), H * D, T * H * D, D, B, H, 3), "attention dK");
                 push_grad(m_k, dk);
             }
         }

@@ -131,6 +131,18 @@ GCB_API int gcb_gemm_batched_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, in
                          float beta, float* C, int64_t ldc, int64_t c_stride_outer, int64_t c_stride_inner,
                          int64_t batch_outer, int64_t batch_inner);
 
+/* The same with a triangular structure the attention GEMMs of a causal model have (no counterpart in the reference, which
+ * multiplies the full T x T matrices): causal = 1: only the part of C on or below the diagonal is needed (M == N; tiles
+ * entirely above it are left untouched — the causal softmax never reads them); causal = 2: op(A)[m, k] is zero for k > m
+ * (probabilities times values: the K loop stops at the diagonal); causal = 3: op(A)[m, k] is zero for k < m (transposed
+ * probabilities: the K loop starts at the diagonal).  causal = 0 is gcb_gemm_batched_f32.  Results equal the full product
+ * wherever it is defined; only work on known zeros is skipped. */
+GCB_API int gcb_gemm_batched_causal_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha,
+                                const float* A, int64_t lda, int64_t a_stride_outer, int64_t a_stride_inner,
+                                const float* B, int64_t ldb, int64_t b_stride_outer, int64_t b_stride_inner,
+                                float beta, float* C, int64_t ldc, int64_t c_stride_outer, int64_t c_stride_inner,
+                                int64_t batch_outer, int64_t batch_inner, int causal);
+
 /* Measurement aid (the reference times with std::chrono around whole loops, benchmarks/bench_kernels.cpp:10-27):
  * between begin and end every GEMM launch is bracketed by CUDA events on the compute stream; end synchronises and
  * returns the number of launches, their summed device time and their algorithmic FLOPs (2*M*N*K*batches). */

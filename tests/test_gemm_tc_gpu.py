@@ -107,3 +107,36 @@ def test_unaligned_operands_fall_back_or_fail_loudly(env):
     assert ctx.ctx_last_gemm_engine() == 1
     assert max_abs_rel(C.cpu().numpy(), A.astype(np.float64) @ B.astype(np.float64)) < 1e-5
     ctx.ctx_set_gemm_engine(2)
+
+
+@pytest.mark.parametrize("engine", [2, 1])
+def test_causal_batched_gemms_skip_only_known_zeros(env, engine):
+    ctx, torch, capi = env
+    ctx.ctx_set_gemm_engine(engine)
+    try:
+        Bn, H, T, D = 2, 2, 384, 64
+        C = H * D
+        q, k, v = rnd(20, Bn, T, C), rnd(21, Bn, T, C), rnd(22, Bn, T, C)
+        Q, Kd, Vd = (torch.from_numpy(x).cuda() for x in (q, k, v))
+        heads = lambda a: a.reshape(Bn, T, H, D).transpose(0, 2, 1, 3).astype(np.float64)
+        S = torch.full((Bn * H, T, T), float("nan"), device="cuda")  # poison: skipped tiles must never be read downstream
+        ctx.gemm_batched_causal_f32(0, 1, T, T, D, 1.0, Q, C, T * C, D, Kd, C, T * C, D, 0.0, S, T, H * T * T, T * T, Bn, H, 1)
+        ctx.sync()
+        s = S.cpu().numpy().reshape(Bn, H, T, T)
+        ref = heads(q) @ heads(k).transpose(0, 1, 3, 2)
+        low = np.tril(np.ones((T, T), bool))
+        assert float(np.abs(s[..., low] - ref[..., low]).max() / np.abs(ref).max()) < TOL
+        ctx.causal_softmax_fwd_f32(S, S, 0.125, Bn * H * T, T)
+        ctx.sync()
+        p = S.cpu().numpy().reshape(Bn, H, T, T).astype(np.float64)
+        assert np.isfinite(p).all() and np.all(np.triu(p, 1) == 0)
+        O = torch.zeros(Bn, T, C, device="cuda")
+        ctx.gemm_batched_causal_f32(0, 0, T, D, T, 1.0, S, T, H * T * T, T * T, Vd, C, T * C, D, 0.0, O, C, T * C, D, Bn, H, 2)
+        dV = torch.zeros(Bn, T, C, device="cuda")
+        ctx.gemm_batched_causal_f32(1, 0, T, D, T, 1.0, S, T, H * T * T, T * T, Q, C, T * C, D, 0.0, dV, C, T * C, D, Bn, H, 3)
+        ctx.sync()
+        untok = lambda a: a.transpose(0, 2, 1, 3).reshape(Bn, T, C)
+        assert max_abs_rel(O.cpu().numpy(), untok(p @ heads(v))) < TOL
+        assert max_abs_rel(dV.cpu().numpy(), untok(p.transpose(0, 1, 3, 2) @ heads(q))) < TOL
+    finally:
+        ctx.ctx_set_gemm_engine(2)
