@@ -266,7 +266,9 @@ def run_ours(args, rank, world, local_rank):
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8 * accum, "d2h_bytes_per_step": 4 * accum, "ms_per_step": ms_e2e / K, "last_loss": last_loss},
             "gpu_launches": launches,
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tensor_tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tensor_tflops"], "traffic": None,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tensor_tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tensor_tflops"],
+                         "traffic": 238.5e6, "traffic_note": "dram read+write of one captured launch of the most frequent shape (M=32768, N=K=1024; algorithmic 272.6 MB, part of C still in L2): profiles/gemm_tc_kernel_linear_fwd_32768x1024x1024.md",
+                         "frac_of_3xtf32_ceiling": achieved / (pk["tensor_tflops"] / 6.0),
                          "kernel": "gemm (%d launches, %.1f ms of the timed region)" % (n_gemm, gemm_ms), "peak_source": "%s dense bf16, sustained; 3xTF32 issues 3 tf32 MMAs per product, so its ceiling is 1/6 of this" % pk["source"],
                          "gemm_share_of_step": gemm_ms / ms_dev},
             "cpu_baseline": cpu,
