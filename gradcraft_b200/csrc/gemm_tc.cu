@@ -363,6 +363,272 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
     }
 }
 
+// ---- CTA-pair variant (cta_group::2): a 256 x 256 tile per pair of SMs --------------------------------------------------
+// Why: with three TF32 products per K step the single-CTA kernel saturates the shared-memory pipe (operand reads by the
+// tensor core + the splitter's traffic) at ~61 % tensor-pipe activity.  In a pair each CTA stages its own 128 rows of A but
+// only HALF of the B tile (128 of the 256 columns); the pair's MMA (M = 256, issued by the even CTA) reads both halves, so
+// per SM the B traffic — TMA fill, splitter, tensor-core reads — is halved.
+// Protocol: full[s] is local to each CTA (its own TMA bytes).  Splitter warps of BOTH CTAs arrive on the leader's conv[s]
+// (8 arrivals, the peer's through mapa + a cluster-scope arrive).  The leader's commits are multicast to both CTAs'
+// empty[s] / acc_full[b] barriers; epilogue warps of both CTAs arrive on the leader's acc_empty[b].
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_on_cta(uint32_t local_bar, uint32_t cta) {
+    asm volatile("{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\tmbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}" ::"r"(local_bar), "r"(cta) : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {  // arrives on the barrier at this offset in both CTAs of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+
+struct PairSmem {
+    static constexpr int BN = 256, STAGES = 6;
+    static constexpr int A_BYTES = TC_BM * TC_BK * 4;        // this CTA's 128 rows
+    static constexpr int B_BYTES = (BN / 2) * TC_BK * 4;     // this CTA's half of the B tile
+    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    static constexpr int EPI_PITCH = 36;
+    static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + 1024 + 256;
+};
+
+__device__ __forceinline__ TileCoord pair_tile_coord(const TcParams& p, int64_t w) {
+    TileCoord t;
+    const int per_batch = p.tiles_n * p.tiles_m;  // tiles_m counts 256-row pair tiles here
+    int r = (int)(w % per_batch); w /= per_batch;
+    const int batch = (int)(w % p.batches); w /= p.batches;
+    t.split = (int)w;
+    constexpr int GROUP = TC_GROUP_M / 2;
+    const int panel = r / (GROUP * p.tiles_n);
+    r -= panel * GROUP * p.tiles_n;
+    const int gm = min(GROUP, p.tiles_m - panel * GROUP);
+    const int tile_m = panel * GROUP + r % gm, tile_n = r / gm;
+    t.m0 = tile_m * 256; t.n0 = tile_n * 256;
+    t.b_out = batch / p.batch_inner; t.b_in = batch % p.batch_inner;
+    t.kb0 = t.split * p.k_blocks_per_split;
+    int kb1 = min(p.k_blocks_total, t.kb0 + p.k_blocks_per_split);
+    t.skip = false;
+    if (p.causal == 1) t.skip = t.n0 >= t.m0 + 256;
+    else if (p.causal == 2) kb1 = min(kb1, (t.m0 + 256 + TC_BK - 1) / TC_BK);
+    else if (p.causal == 3) t.kb0 = max(t.kb0, t.m0 / TC_BK);
+    t.nkb = kb1 - t.kb0;
+    return t;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+    using S = PairSmem;
+    constexpr int BN = S::BN, NST = S::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + S::BAR_OFFSET;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto conv_bar = [&](int s) { return bars + 8u * (NST + s); };
+    auto empty_bar = [&](int s) { return bars + 8u * (2 * NST + s); };
+    auto acc_full_bar = [&](int b) { return bars + 8u * (3 * NST + b); };
+    auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * NST + 2 + b); };
+    const uint32_t tmem_slot = bars + 8u * (3 * NST + 4);
+    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen_base + S::BAR_OFFSET + 8 * (3 * NST + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader (issues the MMAs), 1 = peer
+    const int64_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(conv_bar(s), 8); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers are initialised before anyone arrives on a remote one
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    if (warp == 0) {
+        // ---------------- producer (each CTA: its 128 rows of A, its 128 columns of B) ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
+                const TileCoord tc = pair_tile_coord(p, w);
+                if (tc.skip) continue;
+                const int m0 = tc.m0 + 128 * (int)rank, n0 = tc.n0 + 128 * (int)rank;
+                for (int i = 0; i < tc.nkb; ++i, ++it) {
+                    const int s = it % NST;
+                    const uint32_t ph = (it / NST) & 1u;
+                    ok = mbar_wait(empty_bar(s), ph ^ 1u, p.status, 11);
+                    if (!ok) break;
+                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
+                    mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES);
+                    const int k0 = (tc.kb0 + i) * TC_BK;
+                    if (A_MN) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) tma_load_4d(sa + c * 2048, &map_a, full_bar(s), m0 + 32 * c, k0, tc.b_in, tc.b_out);
+                    } else {
+                        tma_load_4d(sa, &map_a, full_bar(s), k0, m0, tc.b_in, tc.b_out);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) tma_load_4d(sb + c * 2048, &map_b, full_bar(s), n0 + 32 * c, k0, tc.b_in, tc.b_out);
+                    } else {
+                        tma_load_4d(sb, &map_b, full_bar(s), k0, n0, tc.b_in, tc.b_out);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the leader CTA only ----------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            uint32_t it = 0, lt = 0;
+            bool ok = true;
+            for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
+                const TileCoord tc = pair_tile_coord(p, w);
+                if (tc.skip) continue;
+                const uint32_t buf = lt & 1u;
+                ok = mbar_wait(acc_empty_bar(buf), ((lt >> 1) & 1u) ^ 1u, p.status, 15);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int i = 0; i < tc.nkb; ++i, ++it) {
+                    const int s = it % NST;
+                    const uint32_t ph = (it / NST) & 1u;
+                    ok = mbar_wait(conv_bar(s), ph, p.status, 12);  // both CTAs' tiles landed and were split
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
+#pragma unroll
+                    for (int j = 0; j < TC_BK / 8; ++j) {
+                        const uint32_t a_off = A_MN ? j * 1024 : j * 32, b_off = B_MN ? j * 1024 : j * 32;
+                        const uint64_t a_big = A_MN ? make_desc(sa + a_off, 2048, 512, 1) : make_desc(sa + a_off, 16, 512, 4);
+                        const uint64_t a_sml = A_MN ? make_desc(sa + S::A_BYTES + a_off, 2048, 512, 1) : make_desc(sa + S::A_BYTES + a_off, 16, 512, 4);
+                        const uint64_t b_big = B_MN ? make_desc(sb + b_off, 2048, 512, 1) : make_desc(sb + b_off, 16, 512, 4);
+                        const uint64_t b_sml = B_MN ? make_desc(sb + S::B_BYTES + b_off, 2048, 512, 1) : make_desc(sb + S::B_BYTES + b_off, 16, 512, 4);
+                        umma_tf32_pair(d_tmem, a_sml, b_big, idesc, (i | j) ? 1u : 0u);
+                        umma_tf32_pair(d_tmem, a_big, b_sml, idesc, 1u);
+                        umma_tf32_pair(d_tmem, a_big, b_big, idesc, 1u);
+                    }
+                    umma_commit_pair(empty_bar(s));
+                }
+                if (ok) umma_commit_pair(acc_full_bar(buf));
+                ++lt;
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- splitter (own A rows, own half of B) ----------------
+        const int t = threadIdx.x - 64;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
+            const TileCoord tc = pair_tile_coord(p, w);
+            if (tc.skip) continue;
+            for (int i = 0; i < tc.nkb; ++i, ++it) {
+                const int s = it % NST;
+                const uint32_t ph = (it / NST) & 1u;
+                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, 13)) != 0;
+                if (!ok) break;
+                float4* stage = reinterpret_cast<float4*>(gen_base + s * S::STAGE_BYTES);
+                auto split_tile = [&](float4* big, int n_vec) {
+#pragma unroll
+                    for (int q = 0; q < n_vec / 128; ++q) {
+                        const float4 x = big[t + 128 * q];
+                        big[t + 128 * q + n_vec] = make_float4(round_tf32(x.x - trunc_tf32(x.x)), round_tf32(x.y - trunc_tf32(x.y)), round_tf32(x.z - trunc_tf32(x.z)), round_tf32(x.w - trunc_tf32(x.w)));
+                    }
+                };
+                split_tile(stage, S::A_BYTES / 16);
+                split_tile(stage + 2 * (S::A_BYTES / 16), S::B_BYTES / 16);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_on_cta(conv_bar(s), 0);  // the leader's barrier counts both CTAs' splitter warps
+            }
+        }
+    } else {
+        // ---------------- epilogue: this CTA's 128 rows of the pair tile ----------------
+        const int q = warp & 3;
+        float* stg = reinterpret_cast<float*>(gen_base + NST * S::STAGE_BYTES) + q * 32 * S::EPI_PITCH;
+        const bool to_partial = p.splits > 1;
+        const bool vec_ok = to_partial ? (p.N % 4 == 0) : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
+        const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
+        const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;
+        uint32_t lt = 0;
+        bool ok = true;
+        for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
+            const TileCoord tc = pair_tile_coord(p, w);
+            if (tc.skip) continue;
+            const uint32_t buf = lt & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 14)) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float* cbase = to_partial ? p.partial + (int64_t)tc.split * p.M * p.N : p.C + (int64_t)tc.b_out * p.c_so + (int64_t)tc.b_in * p.c_si;
+            const int64_t ld = to_partial ? p.N : p.ldc;
+            const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
+            const float* bias = to_partial ? nullptr : p.bias;
+            const int64_t mrow0 = (int64_t)tc.m0 + 128 * (int)rank + 32 * q;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int64_t nb = (int64_t)tc.n0 + 32 * c;
+                if (nb >= p.N) break;
+                float v[32];
+                tmem_ld32(tmem_base + buf * BN + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), v);
+#pragma unroll
+                for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(stg + lane * S::EPI_PITCH + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                __syncwarp();
+#pragma unroll
+                for (int r4 = 0; r4 < 8; ++r4) {
+                    const int row = r4 * 4 + sub_r;
+                    const int64_t m = mrow0 + row, n = nb + sub_c;
+                    if (m < p.M && n < p.N) {
+                        float4 o = *reinterpret_cast<const float4*>(stg + row * S::EPI_PITCH + sub_c);
+                        o.x *= alpha; o.y *= alpha; o.z *= alpha; o.w *= alpha;
+                        float* dst = cbase + m * ld + n;
+                        if (vec_ok && n + 3 < p.N) {
+                            if (bias) {
+                                const float4 bb = bias_vec ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(bias[n], bias[n + 1], bias[n + 2], bias[n + 3]);
+                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                            }
+                            if (beta != 0.0f) { const float4 old = ld4(dst); o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w; }
+                            st4(dst, o);
+                        } else {
+                            const float ov[4] = {o.x, o.y, o.z, o.w};
+                            for (int u = 0; u < 4; ++u) {
+                                if (n + u < p.N) {
+                                    float r = ov[u];
+                                    if (bias) r += bias[n + u];
+                                    if (beta != 0.0f) r += beta * dst[u];
+                                    dst[u] = r;
+                                }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_on_cta(acc_empty_bar(buf), 0);
+            ++lt;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();  // neither CTA may leave (or free TMEM) while its partner can still touch its memory or barriers
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+    }
+}
+
 // C = alpha * sum_s partial[s] + beta * C + bias, slices added in ascending order
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(float* __restrict__ C, const float* __restrict__ partial, const float* __restrict__ bias, int64_t M, int64_t N, int64_t ldc, int splits,
                                                             float alpha, float beta) {
@@ -443,22 +709,62 @@ static int launch_bn(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, cons
     return GCB_OK;
 }
 
+static int launch_pair(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
+    const size_t smem = PairSmem::TOTAL;
+    cudaLaunchConfig_t cfg = {};
+    const int64_t pairs = std::min<int64_t>(p.work_items, kSMs / 2);
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(TC_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define GCB_PAIR(AM, BMN)                                                                                                   \
+    do {                                                                                                                    \
+        auto kfn = gemm_tc_pair_kernel<AM, BMN>;                                                                            \
+        static bool attr_done = false;                                                                                      \
+        static int max_clusters = 0;                                                                                        \
+        if (!attr_done) {                                                                                                   \
+            GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));              \
+            cfg.gridDim = dim3(kSMs, 1, 1);                                                                                 \
+            GCB_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&max_clusters, kfn, &cfg)); /* pairs that can be co-resident */   \
+            if (max_clusters < 1) { set_error("gemm (pair): no cluster of two CTAs fits on this device"); return GCB_UNSUPPORTED; } \
+            attr_done = true;                                                                                               \
+        }                                                                                                                   \
+        cfg.gridDim = dim3((unsigned)(2 * std::min<int64_t>(p.work_items, max_clusters)), 1, 1);                            \
+        GCB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kfn, ma, mb, p));                                                           \
+    } while (0)
+    if (ta && !tb) GCB_PAIR(true, true);
+    else if (ta && tb) GCB_PAIR(true, false);
+    else if (!ta && !tb) GCB_PAIR(false, true);
+    else GCB_PAIR(false, false);
+#undef GCB_PAIR
+    return GCB_OK;
+}
+
 int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     EncodeTiledFn enc = get_encode(ctx);
     if (!enc) return GCB_UNSUPPORTED;
     cudaSetDevice(ctx->device);
     const int64_t batches = g.batch_outer * g.batch_inner;
     const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+    static const int pair_env = [] { const char* e = getenv("GRADC_TC_PAIR"); return e ? atoi(e) : 1; }();
+    const bool use_pair = pair_env != 0 && BN == 256 && g.M > 128;
     CUtensorMap ma, mb;
     if (!encode_operand(enc, &ma, g.A, ta, g.M, g.K, g.lda, g.a_si, g.a_so, g.batch_inner, g.batch_outer, TC_BM)) return GCB_UNSUPPORTED;
-    if (!encode_operand(enc, &mb, g.B, !tb, g.N, g.K, g.ldb, g.b_si, g.b_so, g.batch_inner, g.batch_outer, BN)) return GCB_UNSUPPORTED;
+    if (!encode_operand(enc, &mb, g.B, !tb, g.N, g.K, g.ldb, g.b_si, g.b_so, g.batch_inner, g.batch_outer, use_pair ? 128 : BN)) return GCB_UNSUPPORTED;
     TcParams p;
     p.M = g.M; p.N = g.N; p.K = g.K;
     p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.C = g.C;
     p.ldc = g.ldc; p.c_so = g.c_so; p.c_si = g.c_si;
     p.batch_inner = (int)g.batch_inner;
     p.tiles_n = (int)((g.N + BN - 1) / BN);
-    p.tiles_m = (int)((g.M + TC_BM - 1) / TC_BM);
+    p.tiles_m = use_pair ? (int)((g.M + 255) / 256) : (int)((g.M + TC_BM - 1) / TC_BM);
     p.k_blocks_total = (int)((g.K + TC_BK - 1) / TC_BK);
     p.status = ctx->d_status;
     const int64_t tiles = (int64_t)p.tiles_n * p.tiles_m * batches;
@@ -467,7 +773,7 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     // (rounds of 148 persistent CTAs x K blocks per slice, plus writing and re-reading the partial tiles)
     int splits = 1;
     if (batches == 1 && p.k_blocks_total >= 64) {
-        const int ctas = kSMs * (BN == 64 ? 2 : 1);
+        const int ctas = use_pair ? kSMs / 2 : kSMs * (BN == 64 ? 2 : 1);
         double best = 1e30;
         for (int sp = 1; sp <= 32 && p.k_blocks_total / sp >= 16; ++sp) {
             const int kbs = (p.k_blocks_total + sp - 1) / sp;
@@ -493,7 +799,8 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     p.split_mode = split_mode_env;
     dim3 grid((unsigned)std::min<int64_t>(p.work_items, (int64_t)kSMs * (BN == 64 ? 2 : 1)), 1, 1);
     int rc;
-    if (BN == 256) rc = launch_bn<256>(ctx, ta, tb, ma, mb, p, grid);
+    if (use_pair) rc = launch_pair(ctx, ta, tb, ma, mb, p);
+    else if (BN == 256) rc = launch_bn<256>(ctx, ta, tb, ma, mb, p, grid);
     else if (BN == 128) rc = launch_bn<128>(ctx, ta, tb, ma, mb, p, grid);
     else rc = launch_bn<64>(ctx, ta, tb, ma, mb, p, grid);
     if (rc) return rc;
