@@ -27,7 +27,7 @@ namespace gcb {
 
 constexpr int TC_BM = 128, TC_BK = 16;
 constexpr int TC_THREADS = 320;  // producer, issuer, 4 splitter warps, 4 epilogue warps
-constexpr uint32_t kSpinLimit = 1u << 24;  // ~16M polls (each >= tens of ns): seconds, far beyond any legitimate wait
+constexpr uint32_t kSpinLimit = 1u << 18;  // polls of up to ~20 us each: seconds in total, far beyond any legitimate wait
 
 struct TcParams {
     int64_t M, N, K;
@@ -51,16 +51,17 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+// try_wait with a suspend-time hint: the thread is parked by the hardware until the phase completes or ~20 us pass, so a
+// waiting role does not burn issue slots that the working roles of the same scheduler need.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity), "r"(20000u) : "memory");
     return ok != 0;
 }
 // Bounded wait.  Returns false when it gave up (and records where).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int where) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 1024) __nanosleep(64);
     }
     atomicExch(&status[0], 1);
     atomicExch(&status[1], where);
@@ -106,7 +107,7 @@ __device__ __forceinline__ float trunc_tf32(float x) { return __uint_as_float(__
 
 template <int BN>
 struct TcSmem {
-    static constexpr int STAGES = BN == 64 ? 3 : 4;  // the narrow tile keeps two CTAs per SM resident
+    static constexpr int STAGES = BN == 64 ? 3 : 4;  // narrow tiles: two CTAs per SM (two issuer / producer threads) beat one deeper ring (measured)
     static constexpr int A_BYTES = TC_BM * TC_BK * 4;  // 8 KB
     static constexpr int B_BYTES = BN * TC_BK * 4;
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;  // big + small of each operand
@@ -319,29 +320,33 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
 #pragma unroll
                 for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(stg + lane * S::EPI_PITCH + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
                 __syncwarp();
+                {
+                    const int64_t m_first = ((int64_t)tc.m0 + 32 * q) + sub_r, n = nb + sub_c;
+                    float* dst = cbase + m_first * ld + n;
+                    const float* src = stg + sub_r * S::EPI_PITCH + sub_c;
+                    if (vec_ok && ((int64_t)tc.m0 + 32 * q) + 32 <= p.M && nb + 32 <= p.N) {  // whole 32 x 32 block in bounds: pointer-increment fast path
+                        float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (bias) bb = bias_vec ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(bias[n], bias[n + 1], bias[n + 2], bias[n + 3]);
+                        const int64_t step = 4 * ld;
 #pragma unroll
-                for (int r4 = 0; r4 < 8; ++r4) {
-                    const int row = r4 * 4 + sub_r;
-                    const int64_t m = (int64_t)tc.m0 + 32 * q + row, n = nb + sub_c;
-                    if (m < p.M && n < p.N) {
-                        float4 o = *reinterpret_cast<const float4*>(stg + row * S::EPI_PITCH + sub_c);
-                        o.x *= alpha; o.y *= alpha; o.z *= alpha; o.w *= alpha;
-                        float* dst = cbase + m * ld + n;
-                        if (vec_ok && n + 3 < p.N) {
-                            if (bias) {
-                                const float4 bb = bias_vec ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(bias[n], bias[n + 1], bias[n + 2], bias[n + 3]);
-                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
-                            }
-                            if (beta != 0.0f) { const float4 old = ld4(dst); o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w; }
+                        for (int r4 = 0; r4 < 8; ++r4, dst += step, src += 4 * S::EPI_PITCH) {
+                            float4 o = *reinterpret_cast<const float4*>(src);
+                            o.x = fmaf(o.x, alpha, bb.x); o.y = fmaf(o.y, alpha, bb.y); o.z = fmaf(o.z, alpha, bb.z); o.w = fmaf(o.w, alpha, bb.w);
+                            if (beta != 0.0f) { const float4 old = ld4(dst); o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y); o.z = fmaf(beta, old.z, o.z); o.w = fmaf(beta, old.w, o.w); }
                             st4(dst, o);
-                        } else {
-                            const float ov[4] = {o.x, o.y, o.z, o.w};
+                        }
+                    } else {
+                        for (int r4 = 0; r4 < 8; ++r4) {
+                            const int64_t m = m_first + 4 * r4;
+                            if (m >= p.M) break;
+                            float* d = cbase + m * ld + n;
+                            const float* sp = src + r4 * 4 * S::EPI_PITCH;
                             for (int u = 0; u < 4; ++u) {
                                 if (n + u < p.N) {
-                                    float r = ov[u];
+                                    float r = sp[u] * alpha;
                                     if (bias) r += bias[n + u];
-                                    if (beta != 0.0f) r += beta * dst[u];
-                                    dst[u] = r;
+                                    if (beta != 0.0f) r += beta * d[u];
+                                    d[u] = r;
                                 }
                             }
                         }
@@ -584,29 +589,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
 #pragma unroll
                 for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(stg + lane * S::EPI_PITCH + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
                 __syncwarp();
+                {
+                    const int64_t m_first = mrow0 + sub_r, n = nb + sub_c;
+                    float* dst = cbase + m_first * ld + n;
+                    const float* src = stg + sub_r * S::EPI_PITCH + sub_c;
+                    if (vec_ok && mrow0 + 32 <= p.M && nb + 32 <= p.N) {  // whole 32 x 32 block in bounds: pointer-increment fast path
+                        float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (bias) bb = bias_vec ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(bias[n], bias[n + 1], bias[n + 2], bias[n + 3]);
+                        const int64_t step = 4 * ld;
 #pragma unroll
-                for (int r4 = 0; r4 < 8; ++r4) {
-                    const int row = r4 * 4 + sub_r;
-                    const int64_t m = mrow0 + row, n = nb + sub_c;
-                    if (m < p.M && n < p.N) {
-                        float4 o = *reinterpret_cast<const float4*>(stg + row * S::EPI_PITCH + sub_c);
-                        o.x *= alpha; o.y *= alpha; o.z *= alpha; o.w *= alpha;
-                        float* dst = cbase + m * ld + n;
-                        if (vec_ok && n + 3 < p.N) {
-                            if (bias) {
-                                const float4 bb = bias_vec ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(bias[n], bias[n + 1], bias[n + 2], bias[n + 3]);
-                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
-                            }
-                            if (beta != 0.0f) { const float4 old = ld4(dst); o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w; }
+                        for (int r4 = 0; r4 < 8; ++r4, dst += step, src += 4 * S::EPI_PITCH) {
+                            float4 o = *reinterpret_cast<const float4*>(src);
+                            o.x = fmaf(o.x, alpha, bb.x); o.y = fmaf(o.y, alpha, bb.y); o.z = fmaf(o.z, alpha, bb.z); o.w = fmaf(o.w, alpha, bb.w);
+                            if (beta != 0.0f) { const float4 old = ld4(dst); o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y); o.z = fmaf(beta, old.z, o.z); o.w = fmaf(beta, old.w, o.w); }
                             st4(dst, o);
-                        } else {
-                            const float ov[4] = {o.x, o.y, o.z, o.w};
+                        }
+                    } else {
+                        for (int r4 = 0; r4 < 8; ++r4) {
+                            const int64_t m = m_first + 4 * r4;
+                            if (m >= p.M) break;
+                            float* d = cbase + m * ld + n;
+                            const float* sp = src + r4 * 4 * S::EPI_PITCH;
                             for (int u = 0; u < 4; ++u) {
                                 if (n + u < p.N) {
-                                    float r = ov[u];
+                                    float r = sp[u] * alpha;
                                     if (bias) r += bias[n + u];
-                                    if (beta != 0.0f) r += beta * dst[u];
-                                    dst[u] = r;
+                                    if (beta != 0.0f) r += beta * d[u];
+                                    d[u] = r;
                                 }
                             }
                         }
@@ -754,7 +763,7 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     const int64_t batches = g.batch_outer * g.batch_inner;
     const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
     static const int pair_env = [] { const char* e = getenv("GRADC_TC_PAIR"); return e ? atoi(e) : 1; }();
-    const bool use_pair = pair_env != 0 && BN == 256 && g.M > 128;
+    const bool use_pair = pair_env != 0 && BN == 256 && g.M > 128 && g.K >= 256;  // short K loops are epilogue-bound: nothing to gain from sharing B
     CUtensorMap ma, mb;
     if (!encode_operand(enc, &ma, g.A, ta, g.M, g.K, g.lda, g.a_si, g.a_so, g.batch_inner, g.batch_outer, TC_BM)) return GCB_UNSUPPORTED;
     if (!encode_operand(enc, &mb, g.B, !tb, g.N, g.K, g.ldb, g.b_si, g.b_so, g.batch_inner, g.batch_outer, use_pair ? 128 : BN)) return GCB_UNSUPPORTED;
