@@ -73,5 +73,35 @@ def build_trainer(verbose=False, force=False):
     return TRAINER_LIB
 
 
+TRAIN_BIN = os.path.join(OBJ, "train_ref")
+
+
+def build_reference_train(reference_root="/root/reference", verbose=False):
+    """Compiles the reference's own train.cpp, unchanged, against gradcraft_b200/gradc and links it with the sm_100a backend.
+    The source is read where it lies (a scratch copy is needed only because a quoted include searches the including file's
+    directory first); nothing of it is stored in this repository.  Returns the binary's path, or None without the reference."""
+    import shutil
+    import tempfile
+
+    src = os.path.join(reference_root, "train.cpp")
+    if not os.path.exists(src):
+        return TRAIN_BIN if os.path.exists(TRAIN_BIN) else None
+    hdrs = tuple(os.path.join(HERE, "gradc", f) for f in os.listdir(os.path.join(HERE, "gradc")))
+    if not _newer(src, TRAIN_BIN, hdrs + (LIB,)):
+        return TRAIN_BIN
+    os.makedirs(OBJ, exist_ok=True)
+    with tempfile.TemporaryDirectory() as tmp:
+        shutil.copy(src, os.path.join(tmp, "train.cpp"))
+        cmd = ["g++", "-std=c++23", "-O2", "-I", HERE, "-I/usr/local/cuda/include", os.path.join(tmp, "train.cpp"), "-o", TRAIN_BIN,
+               "-L" + HERE, "-lgradc_b200", "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath," + HERE, "-Wl,-rpath,/usr/local/cuda/lib64"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("train.cpp did not build against the host API:\n" + r.stderr[-6000:])
+    if verbose:
+        print("built", TRAIN_BIN)
+    return TRAIN_BIN
+
+
 if __name__ == "__main__":
     build(verbose=True, force="--force" in sys.argv)
+    build_reference_train(verbose=True)

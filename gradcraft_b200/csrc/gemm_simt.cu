@@ -53,12 +53,16 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs g) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
 
-    load_tiles(0);
+    // causal operands: skip the K range where op(A) is known to be zero (same 128-row granularity as the tensor-core engine)
+    int64_t k_begin = 0, k_end = g.K;
+    if (g.causal == 2) k_end = min(g.K, m0 + BM);
+    else if (g.causal == 3) k_begin = min(g.K, m0) / BK * BK;
+    load_tiles(k_begin);
     store_tiles(0);
     __syncthreads();
     int buf = 0;
-    for (int64_t k0 = 0; k0 < g.K; k0 += BK) {
-        const bool more = k0 + BK < g.K;
+    for (int64_t k0 = k_begin; k0 < k_end; k0 += BK) {
+        const bool more = k0 + BK < k_end;
         if (more) load_tiles(k0 + BK);
 #pragma unroll
         for (int k = 0; k < BK; ++k) {

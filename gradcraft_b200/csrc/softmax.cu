@@ -16,7 +16,7 @@ int launch_sum_partials(gcb_ctx* ctx, float* out, const float* partial, int coun
 constexpr int kSmWarps = 8;
 
 template <int NCHUNK>
-__global__ void __launch_bounds__(kSmWarps * 32) causal_softmax_fwd_warp(float* __restrict__ probs, const float* __restrict__ scores, float scale, int64_t rows, int T) {
+__global__ void __launch_bounds__(kSmWarps * 32) causal_softmax_fwd_warp(float* __restrict__ probs, const float* __restrict__ scores, float scale, int64_t rows, int T, int band) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * kSmWarps + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kSmWarps;
@@ -49,17 +49,18 @@ __global__ void __launch_bounds__(kSmWarps * 32) causal_softmax_fwd_warp(float* 
         sum = warp_sum(sum);
         const float inv = 1.0f / sum;
         float* pr = probs + r * T;
+        const int limit = band ? min(T, (i / band + 1) * band) : T;  // zeros are written up to the end of the diagonal block only
 #pragma unroll
         for (int k = 0; k < NCHUNK; ++k) {
             const int c = (lane + 32 * k) * 4;
-            if (c < T) st4(pr + c, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv));
+            if (c < limit) st4(pr + c, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv));
         }
     }
 }
 
 template <int NCHUNK>
 __global__ void __launch_bounds__(kSmWarps * 32, (NCHUNK == 8 ? 3 : 4)) causal_softmax_bwd_warp(float* __restrict__ ds, const float* __restrict__ dp, const float* __restrict__ probs, float scale,
-                                                                         int64_t rows, int T, int accumulate) {
+                                                                         int64_t rows, int T, int accumulate, int band) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * kSmWarps + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kSmWarps;
@@ -88,10 +89,11 @@ __global__ void __launch_bounds__(kSmWarps * 32, (NCHUNK == 8 ? 3 : 4)) causal_s
         }
         dot = warp_sum(dot);
         float* dr = ds + r * T;
+        const int limit = band ? min(T, (i / band + 1) * band) : T;
 #pragma unroll
         for (int k = 0; k < NCHUNK; ++k) {
             const int c = (lane + 32 * k) * 4;
-            if (c < T) {
+            if (c < limit) {
                 float4 o = make_float4(scale * p[k].x * (g[k].x - dot), scale * p[k].y * (g[k].y - dot), scale * p[k].z * (g[k].z - dot), scale * p[k].w * (g[k].w - dot));
                 if (accumulate) {
                     if (c <= i) { const float4 old = ld4(dr + c); o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; st4(dr + c, o); }
@@ -220,7 +222,7 @@ using namespace gcb;
 
 extern "C" {
 
-int gcb_causal_softmax_fwd_f32(gcb_ctx* ctx, float* probs, const float* scores, float scale, int64_t rows, int64_t T) {
+static int csm_fwd(gcb_ctx* ctx, float* probs, const float* scores, float scale, int64_t rows, int64_t T, int band) {
     GCB_REQUIRE(ctx && rows >= 0 && T >= 0 && (rows * T == 0 || (probs && scores)), "gcb_causal_softmax_fwd_f32: bad arguments");
     GCB_REQUIRE(T == 0 || rows % T == 0, "gcb_causal_softmax_fwd_f32: rows (%lld) must be a multiple of seq_len (%lld)", (long long)rows, (long long)T);
     if (rows * T == 0) return GCB_OK;
@@ -228,7 +230,7 @@ int gcb_causal_softmax_fwd_f32(gcb_ctx* ctx, float* probs, const float* scores, 
     if (T % 4 == 0 && T <= 1024 && aligned16(probs) && aligned16(scores)) {
         int64_t blocks = std::min<int64_t>((rows + kSmWarps - 1) / kSmWarps, (int64_t)kSMs * 8);
         const int n = chunks_for(T);
-#define GCB_L(N) causal_softmax_fwd_warp<N><<<(unsigned)blocks, kSmWarps * 32, 0, ctx->stream>>>(probs, scores, scale, rows, (int)T)
+#define GCB_L(N) causal_softmax_fwd_warp<N><<<(unsigned)blocks, kSmWarps * 32, 0, ctx->stream>>>(probs, scores, scale, rows, (int)T, band)
         if (n == 1) GCB_L(1); else if (n == 2) GCB_L(2); else if (n == 4) GCB_L(4); else GCB_L(8);
 #undef GCB_L
     } else {
@@ -237,7 +239,13 @@ int gcb_causal_softmax_fwd_f32(gcb_ctx* ctx, float* probs, const float* scores, 
     return after_launch(ctx, "causal_softmax_fwd");
 }
 
-int gcb_causal_softmax_bwd_f32(gcb_ctx* ctx, float* ds, const float* dp, const float* probs, float scale, int64_t rows, int64_t T, int accumulate) {
+int gcb_causal_softmax_fwd_f32(gcb_ctx* ctx, float* probs, const float* scores, float scale, int64_t rows, int64_t T) { return csm_fwd(ctx, probs, scores, scale, rows, T, 0); }
+int gcb_causal_softmax_fwd_band_f32(gcb_ctx* ctx, float* probs, const float* scores, float scale, int64_t rows, int64_t T, int band) {
+    GCB_REQUIRE(band >= 0 && band % 4 == 0, "gcb_causal_softmax_fwd_band_f32: band must be a non-negative multiple of 4");
+    return csm_fwd(ctx, probs, scores, scale, rows, T, band);
+}
+
+static int csm_bwd(gcb_ctx* ctx, float* ds, const float* dp, const float* probs, float scale, int64_t rows, int64_t T, int accumulate, int band) {
     GCB_REQUIRE(ctx && rows >= 0 && T >= 0 && (rows * T == 0 || (ds && dp && probs)), "gcb_causal_softmax_bwd_f32: bad arguments");
     GCB_REQUIRE(T == 0 || rows % T == 0, "gcb_causal_softmax_bwd_f32: rows (%lld) must be a multiple of seq_len (%lld)", (long long)rows, (long long)T);
     if (rows * T == 0) return GCB_OK;
@@ -245,13 +253,21 @@ int gcb_causal_softmax_bwd_f32(gcb_ctx* ctx, float* ds, const float* dp, const f
     if (T % 4 == 0 && T <= 1024 && aligned16(ds) && aligned16(dp) && aligned16(probs)) {
         int64_t blocks = std::min<int64_t>((rows + kSmWarps - 1) / kSmWarps, (int64_t)kSMs * 8);
         const int n = chunks_for(T);
-#define GCB_L(N) causal_softmax_bwd_warp<N><<<(unsigned)blocks, kSmWarps * 32, 0, ctx->stream>>>(ds, dp, probs, scale, rows, (int)T, accumulate)
+#define GCB_L(N) causal_softmax_bwd_warp<N><<<(unsigned)blocks, kSmWarps * 32, 0, ctx->stream>>>(ds, dp, probs, scale, rows, (int)T, accumulate, band)
         if (n == 1) GCB_L(1); else if (n == 2) GCB_L(2); else if (n == 4) GCB_L(4); else GCB_L(8);
 #undef GCB_L
     } else {
         causal_softmax_bwd_block<<<(unsigned)std::min<int64_t>(rows, (int64_t)kSMs * 8), 256, 0, ctx->stream>>>(ds, dp, probs, scale, rows, T, accumulate);
     }
     return after_launch(ctx, "causal_softmax_bwd");
+}
+
+int gcb_causal_softmax_bwd_f32(gcb_ctx* ctx, float* ds, const float* dp, const float* probs, float scale, int64_t rows, int64_t T, int accumulate) {
+    return csm_bwd(ctx, ds, dp, probs, scale, rows, T, accumulate, 0);
+}
+int gcb_causal_softmax_bwd_band_f32(gcb_ctx* ctx, float* ds, const float* dp, const float* probs, float scale, int64_t rows, int64_t T, int accumulate, int band) {
+    GCB_REQUIRE(band >= 0 && band % 4 == 0, "gcb_causal_softmax_bwd_band_f32: band must be a non-negative multiple of 4");
+    return csm_bwd(ctx, ds, dp, probs, scale, rows, T, accumulate, band);
 }
 
 int gcb_softmax_ce_fwd_f32(gcb_ctx* ctx, float* loss, float* probs, const float* logits, const void* targets, int index_type, int64_t rows, int64_t V, float eps) {

@@ -604,6 +604,9 @@ inline Tensor<float> matmul(Tensor<float> x, Tensor<float> w) { return linear(st
 // q, k, v are read in place through two-level batch strides — the head split reshape+permute of the attention layer
 // stays a view — and the output is laid out (B, T, H, D) in memory, so merging heads is a view as well.
 class SDPANode : public Node<float> {
+    // the causal GEMMs that consume P and dS work on 128-row tiles: zeros above the diagonal are needed inside the 128-wide
+    // diagonal blocks only, so the softmax kernels stop writing there
+    static constexpr int kCausalBand = 128;
     Tensor<float> m_q, m_k, m_v;
     float m_scale;
     int64_t m_B, m_H, m_T, m_D;
@@ -624,7 +627,7 @@ public:
         int64_t qo, qi, ql, ko, ki, kl, vo, vi, vl;
         strides4(m_q, qo, qi, ql); strides4(m_k, ko, ki, kl); strides4(m_v, vo, vi, vl);
         gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_T, T, T, D, 1.0f, m_q.data_ptr(), ql, qo, qi, m_k.data_ptr(), kl, ko, ki, 0.0f, m_probs.data_ptr(), T, H * T * T, T * T, B, H, 1), "attention scores");
-        gcb_check(gcb_causal_softmax_fwd_f32(c, m_probs.data_ptr(), m_probs.data_ptr(), m_scale, B * H * T, T), "causal softmax");
+        gcb_check(gcb_causal_softmax_fwd_band_f32(c, m_probs.data_ptr(), m_probs.data_ptr(), m_scale, B * H * T, T, kCausalBand), "causal softmax");
         Tensor<float> mem({B, T, H, D}, m_q.device(), uninitialized);
         gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_N, T, D, T, 1.0f, m_probs.data_ptr(), T, H * T * T, T * T, m_v.data_ptr(), vl, vo, vi, 0.0f, mem.data_ptr(), H * D, T * H * D, D, B, H, 2), "attention output");
         return Tensor<float>({B, H, T, D}, out_strides(H, T, D), 0, mem._get_storage(), false);
@@ -648,7 +651,7 @@ public:
         if (m_q.requires_grad() || m_k.requires_grad()) {
             Tensor<float> ds({B * H, T, T}, g.device(), uninitialized);  // dP = dO . V^T, then dS in place
             gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_T, T, T, D, 1.0f, g.data_ptr(), gl, go, gi, m_v.data_ptr(), vl, vo, vi, 0.0f, ds.data_ptr(), T, H * T * T, T * T, B, H, 1), "attention dP");
-            gcb_check(gcb_causal_softmax_bwd_f32(c, ds.data_ptr(), ds.data_ptr(), m_probs.data_ptr(), m_scale, B * H * T, T, 0), "causal softmax backward");
+            gcb_check(gcb_causal_softmax_bwd_band_f32(c, ds.data_ptr(), ds.data_ptr(), m_probs.data_ptr(), m_scale, B * H * T, T, 0, kCausalBand), "causal softmax backward");
             if (m_q.requires_grad()) {  // dQ = dS . K
                 Tensor<float> dq = fresh();
                 gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_N, T, D, T, 1.0f, ds.data_ptr(), T, H * T * T, T * T, m_k.data_ptr(), kl, ko, ki, 0.0f, dq.data_ptr(), H * D, T * H * D, D, B, H, 2), "attention dQ");

@@ -196,6 +196,12 @@ GCB_API int gcb_swiglu_bwd_f32(gcb_ctx* ctx, float* da /*opt*/, float* db /*opt*
 GCB_API int gcb_causal_softmax_fwd_f32(gcb_ctx* ctx, float* probs, const float* scores, float scale, int64_t rows, int64_t seq_len);
 GCB_API int gcb_causal_softmax_bwd_f32(gcb_ctx* ctx, float* dscores, const float* dprobs, const float* probs, float scale, int64_t rows, int64_t seq_len, int accumulate);
 
+/* Same kernels for a consumer that skips what causality zeroes (gcb_gemm_batched_causal_f32 with 128-row tiles): with
+ * band > 0 a row is written only up to the end of its band-wide diagonal block (columns < (i / band + 1) * band); what lies
+ * beyond is never read by such a consumer and is left untouched.  band = 0 is the full-row form above. */
+GCB_API int gcb_causal_softmax_fwd_band_f32(gcb_ctx* ctx, float* probs, const float* scores, float scale, int64_t rows, int64_t seq_len, int band);
+GCB_API int gcb_causal_softmax_bwd_band_f32(gcb_ctx* ctx, float* dscores, const float* dprobs, const float* probs, float scale, int64_t rows, int64_t seq_len, int accumulate, int band);
+
 /* ---- loss: apply_sparse_softmax_crossentropy_{forward,backward}, cuda_math.hpp:45-50 ------------ */
 /* probs may alias logits.  *loss = mean_r(-log(p[r, t_r] + eps)), reduced in a fixed order. */
 GCB_API int gcb_softmax_ce_fwd_f32(gcb_ctx* ctx, float* loss_scalar, float* probs, const float* logits, const void* targets, int index_type, int64_t rows, int64_t vocab, float eps);

@@ -482,3 +482,29 @@ def test_arena_reuse_limit_and_errors(env):
     ctx.arena_set_limit(0)
     with pytest.raises(capi.GcbError):
         ctx.gemm_f32(0, 0, 4, 4, 4, 1.0, None, 4, None, 4, 0.0, None, 4, None)
+
+
+@pytest.mark.parametrize("T,band", [(256, 128), (1024, 128), (384, 128), (64, 128)])
+def test_causal_softmax_band_variants(env, T, band):
+    """Band-limited forms: identical on and below the diagonal and inside the diagonal block; nothing is written beyond it."""
+    ctx, torch, capi = env
+    BH = 2
+    s, dp = rnd(90, 1, BH, T, T) * 3, rnd(91, 1, BH, T, T, scale=1e-2)
+    rows = BH * T
+    S = dev(torch, s)
+    P = torch.full((rows, T), 5.0, device="cuda")
+    ctx.causal_softmax_fwd_band_f32(P, S, 0.125, rows, T, band)
+    p = host(ctx, P).reshape(BH, T, T)
+    rp = O.causal_softmax_fwd(s, 0.125)[0]
+    i = np.arange(T)[:, None]
+    j = np.arange(T)[None, :]
+    inside = j < np.minimum(T, (i // band + 1) * band)
+    assert max_abs_rel(np.where(inside, p, 0), np.where(inside, rp, 0)) < TOL
+    assert np.all(p[:, ~inside] == 5.0)  # untouched
+    Pfull = dev(torch, rp.reshape(rows, T))
+    dS = torch.full((rows, T), 5.0, device="cuda")
+    ctx.causal_softmax_bwd_band_f32(dS, dev(torch, dp), Pfull, 0.125, rows, T, 0, band)
+    d = host(ctx, dS).reshape(BH, T, T)
+    rd = O.causal_softmax_bwd(dp, rp[None], 0.125)[0]
+    assert max_abs_rel(np.where(inside, d, 0), np.where(inside, rd, 0)) < TOL
+    assert np.all(d[:, ~inside] == 5.0)
