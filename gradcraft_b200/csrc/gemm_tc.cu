@@ -39,7 +39,9 @@ struct TcParams {
     int tiles_n, tiles_m;
     int k_blocks_per_split, k_blocks_total, splits;
     int batches;
-    int64_t work_items;  // tiles_n * tiles_m * batches * splits
+    int64_t work_items;  // tiles to compute (x splits)
+    int64_t loop_end;    // bound of the persistent loop: work_items, rounded up to whole rounds where the snake order needs it
+    int kept_per_batch;  // causal mode 1: tiles per batch at or below the diagonal
     int causal;          // see GemmArgs::causal
     int split_mode;      // 1 (default): big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
                          // 0: big = rna_tf32(x) written back, small = x - big (does not rely on the hardware's truncation)
@@ -105,6 +107,31 @@ __device__ __forceinline__ float round_tf32(float x) {  // nearest TF32 value, r
 
 __device__ __forceinline__ float trunc_tf32(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 
+// Optional role timing (compile with -DGCB_TC_TRACE): per role, cycles spent waiting on barriers and cycles in total,
+// summed over CTAs into g_tc_trace[2 * role], [2 * role + 1]; roles: 0 producer, 1 issuer, 2 splitter warps, 3 epilogue warps.
+#ifdef GCB_TC_TRACE
+__device__ unsigned long long g_tc_trace[8];
+__device__ __forceinline__ long long tr_clock() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)); return t; }
+struct RoleTrace {
+    long long wait, t0;
+    int slot;
+    __device__ explicit RoleTrace(int s) : wait(0), t0(tr_clock()), slot(s) {}
+    __device__ void done() {
+        if ((threadIdx.x & 31) == 0) {
+            atomicAdd(&g_tc_trace[2 * slot], (unsigned long long)wait);
+            atomicAdd(&g_tc_trace[2 * slot + 1], (unsigned long long)(tr_clock() - t0));
+        }
+    }
+};
+#define TR_BEGIN(s) RoleTrace tr(s)
+#define TR_WAIT(call) [&] { const long long tr_a = tr_clock(); const bool tr_r = (call); tr.wait += tr_clock() - tr_a; return tr_r; }()
+#define TR_END() tr.done()
+#else
+#define TR_BEGIN(s)
+#define TR_WAIT(call) (call)
+#define TR_END()
+#endif
+
 template <int BN>
 struct TcSmem {
     static constexpr int STAGES = BN == 64 ? 3 : 4;  // narrow tiles: two CTAs per SM (two issuer / producer threads) beat one deeper ring (measured)
@@ -122,25 +149,53 @@ struct TileCoord {
     bool skip;
 };
 constexpr int TC_GROUP_M = 16;  // row tiles per raster panel: the panel's A rows and the B tiles it sweeps stay hot in L2
+// Column tiles of row tile i that are not entirely above the diagonal (causal mode 1).
+__host__ __device__ __forceinline__ int causal_kept_cols(int i, int tiles_n, int BN) { return min(tiles_n, ((i + 1) * TC_BM + BN - 1) / BN); }
+
+// Work item w -> tile.  Plain problems: panels of TC_GROUP_M row tiles, batches outermost.  Causal problems are balanced
+// statically, because a CTA's items are c, c + G, c + 2G, ... and G is usually a multiple of the tiles per batch:
+//   mode 1: only the tiles at or below the diagonal are enumerated (equal cost each);
+//   modes 2 / 3: the K range, and so the cost, grows (shrinks) with the row tile.  Items are ordered heaviest first and
+//                dealt out in snake order (left to right, then right to left), so every CTA's total is about the same.
 __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int64_t w, int BN) {
     TileCoord t;
-    const int per_batch = p.tiles_n * p.tiles_m;
-    int r = (int)(w % per_batch); w /= per_batch;
-    const int batch = (int)(w % p.batches); w /= p.batches;
-    t.split = (int)w;
-    const int panel = r / (TC_GROUP_M * p.tiles_n);
-    r -= panel * TC_GROUP_M * p.tiles_n;
-    const int gm = min(TC_GROUP_M, p.tiles_m - panel * TC_GROUP_M);
-    const int tile_m = panel * TC_GROUP_M + r % gm, tile_n = r / gm;
+    t.skip = false;
+    t.split = 0;
+    int tile_m, tile_n, batch;
+    if (p.causal == 1) {
+        int r = (int)(w % p.kept_per_batch);
+        batch = (int)(w / p.kept_per_batch);
+        tile_m = 0;
+        for (int cnt = causal_kept_cols(0, p.tiles_n, BN); r >= cnt; cnt = causal_kept_cols(++tile_m, p.tiles_n, BN)) r -= cnt;
+        tile_n = r;
+    } else if (p.causal == 2 || p.causal == 3) {
+        const int64_t G = gridDim.x, round = w / G, c = w - round * G;
+        const int64_t q = round * G + ((round & 1) ? G - 1 - c : c);
+        t.skip = q >= p.work_items;
+        const int64_t per_class = (int64_t)p.batches * p.tiles_n;
+        const int cls = (int)(q / per_class);
+        const int rem = (int)(q - cls * per_class);
+        tile_m = p.causal == 2 ? p.tiles_m - 1 - cls : cls;
+        tile_n = rem % p.tiles_n;
+        batch = rem / p.tiles_n;
+    } else {
+        const int per_batch = p.tiles_n * p.tiles_m;
+        int r = (int)(w % per_batch); w /= per_batch;
+        batch = (int)(w % p.batches); w /= p.batches;
+        t.split = (int)w;
+        const int panel = r / (TC_GROUP_M * p.tiles_n);
+        r -= panel * TC_GROUP_M * p.tiles_n;
+        const int gm = min(TC_GROUP_M, p.tiles_m - panel * TC_GROUP_M);
+        tile_m = panel * TC_GROUP_M + r % gm; tile_n = r / gm;
+    }
     t.m0 = tile_m * TC_BM; t.n0 = tile_n * BN;
     t.b_out = batch / p.batch_inner; t.b_in = batch % p.batch_inner;
     t.kb0 = t.split * p.k_blocks_per_split;
     int kb1 = min(p.k_blocks_total, t.kb0 + p.k_blocks_per_split);
-    t.skip = false;
-    if (p.causal == 1) t.skip = t.n0 >= t.m0 + TC_BM;                                   // tile entirely above the diagonal
-    else if (p.causal == 2) kb1 = min(kb1, (t.m0 + TC_BM + TC_BK - 1) / TC_BK);           // op(A) is zero right of the diagonal
-    else if (p.causal == 3) t.kb0 = max(t.kb0, t.m0 / TC_BK);                             // op(A) is zero left of the diagonal
+    if (p.causal == 2) kb1 = min(kb1, (t.m0 + TC_BM + TC_BK - 1) / TC_BK);  // op(A) is zero right of the diagonal
+    else if (p.causal == 3) t.kb0 = max(t.kb0, t.m0 / TC_BK);               // op(A) is zero left of the diagonal
     t.nkb = kb1 - t.kb0;
+    if (t.nkb <= 0) t.skip = true;
     return t;
 }
 
@@ -184,13 +239,14 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
         if (lane == 0) {
             uint32_t it = 0;  // running K-block count across tiles: stage = it % STAGES, phase = (it / STAGES) & 1
             bool ok = true;
-            for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
+            TR_BEGIN(0);
+            for (int64_t w = blockIdx.x; w < p.loop_end && ok; w += gridDim.x) {
                 const TileCoord tc = tile_coord(p, w, BN);
                 if (tc.skip) continue;
                 for (int i = 0; i < tc.nkb; ++i, ++it) {
                     const int s = it % TC_STAGES;
                     const uint32_t ph = (it / TC_STAGES) & 1u;
-                    ok = mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1);
+                    ok = TR_WAIT(mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1));
                     if (!ok) break;
                     const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
                     mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES);
@@ -209,6 +265,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                     }
                 }
             }
+            TR_END();
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -217,7 +274,8 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
             uint32_t it = 0, lt = 0;
             bool ok = true;
-            for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
+            TR_BEGIN(1);
+            for (int64_t w = blockIdx.x; w < p.loop_end && ok; w += gridDim.x) {
                 const TileCoord tc = tile_coord(p, w, BN);
                 if (tc.skip) continue;
                 const uint32_t buf = lt & 1u;
@@ -228,8 +286,8 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                 for (int i = 0; i < tc.nkb; ++i, ++it) {
                     const int s = it % TC_STAGES;
                     const uint32_t ph = (it / TC_STAGES) & 1u;
-                    ok = mbar_wait(p.split_mode ? full_bar(s) : conv_bar(s), ph, p.status, 2);
-                    if (ok && p.split_mode) ok = mbar_wait(conv_bar(s), ph, p.status, 2);
+                    ok = TR_WAIT(mbar_wait(p.split_mode ? full_bar(s) : conv_bar(s), ph, p.status, 2));
+                    if (ok && p.split_mode) ok = TR_WAIT(mbar_wait(conv_bar(s), ph, p.status, 2));
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
@@ -249,19 +307,21 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                 if (ok) umma_commit(acc_full_bar(buf));  // fires when every MMA of this tile has completed
                 ++lt;
             }
+            TR_END();
         }
     } else if (warp < 6) {
         // ---------------- splitter ----------------
         const int t = threadIdx.x - 64;  // 0..127
         uint32_t it = 0;
         bool ok = true;
-        for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
+        TR_BEGIN(2);
+        for (int64_t w = blockIdx.x; w < p.loop_end && ok; w += gridDim.x) {
             const TileCoord tc = tile_coord(p, w, BN);
             if (tc.skip) continue;
             for (int i = 0; i < tc.nkb; ++i, ++it) {
                 const int s = it % TC_STAGES;
                 const uint32_t ph = (it / TC_STAGES) & 1u;
-                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, 3)) != 0;
+                ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, 3)) != 0);
                 if (!ok) break;
                 float4* stage = reinterpret_cast<float4*>(gen_base + s * S::STAGE_BYTES);
                 // the twin tile sits one tile size after its source, same (swizzled) position inside the tile
@@ -289,6 +349,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                 if (lane == 0) mbar_arrive(conv_bar(s));
             }
         }
+        TR_END();
     } else {
         // ---------------- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. +31, i.e. 32 rows of the tile ----------------
         const int q = warp & 3;
@@ -299,11 +360,12 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
         const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;  // store phase: 4 rows x 8 float4 per instruction (128 B per row)
         uint32_t lt = 0;
         bool ok = true;
-        for (int64_t w = blockIdx.x; w < p.work_items && ok; w += gridDim.x) {
+        TR_BEGIN(3);
+        for (int64_t w = blockIdx.x; w < p.loop_end && ok; w += gridDim.x) {
             const TileCoord tc = tile_coord(p, w, BN);
             if (tc.skip) continue;
             const uint32_t buf = lt & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0;
+            ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float* cbase = to_partial ? p.partial + (int64_t)tc.split * p.M * p.N : p.C + (int64_t)tc.b_out * p.c_so + (int64_t)tc.b_in * p.c_si;
@@ -359,6 +421,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
             if (lane == 0) mbar_arrive(acc_empty_bar(buf));  // this accumulator may be overwritten
             ++lt;
         }
+        TR_END();
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -781,7 +844,7 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     // split-K when the tiles alone would leave SMs idle: pick the slice count with the lowest modelled time
     // (rounds of 148 persistent CTAs x K blocks per slice, plus writing and re-reading the partial tiles)
     int splits = 1;
-    if (batches == 1 && p.k_blocks_total >= 64) {
+    if (batches == 1 && p.k_blocks_total >= 64 && g.causal == 0) {
         const int ctas = use_pair ? kSMs / 2 : kSMs * (BN == 64 ? 2 : 1);
         double best = 1e30;
         for (int sp = 1; sp <= 32 && p.k_blocks_total / sp >= 16; ++sp) {
@@ -804,9 +867,15 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     p.batches = (int)batches;
     p.causal = g.causal;
     p.work_items = (int64_t)p.tiles_n * p.tiles_m * batches * splits;
+    p.kept_per_batch = 0;
+    if (!use_pair && g.causal == 1) {  // enumerate only the tiles at or below the diagonal
+        for (int i = 0; i < p.tiles_m; ++i) p.kept_per_batch += causal_kept_cols(i, p.tiles_n, BN);
+        p.work_items = (int64_t)p.kept_per_batch * batches;
+    }
     static const int split_mode_env = [] { const char* e = getenv("GRADC_TC_SPLIT_MODE"); return e ? atoi(e) : 1; }();
     p.split_mode = split_mode_env;
     dim3 grid((unsigned)std::min<int64_t>(p.work_items, (int64_t)kSMs * (BN == 64 ? 2 : 1)), 1, 1);
+    p.loop_end = g.causal >= 2 ? (p.work_items + grid.x - 1) / grid.x * grid.x : p.work_items;  // snake order: whole rounds
     int rc;
     if (use_pair) rc = launch_pair(ctx, ta, tb, ma, mb, p);
     else if (BN == 256) rc = launch_bn<256>(ctx, ta, tb, ma, mb, p, grid);
@@ -826,3 +895,12 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
 }
 
 }  // namespace gcb
+
+#ifdef GCB_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int gcb_tc_trace_read(unsigned long long* out8, int reset) {
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(out8, gcb::g_tc_trace, sizeof(unsigned long long) * 8) != cudaSuccess) return 1;
+    if (reset) { unsigned long long z[8] = {}; cudaMemcpyToSymbol(gcb::g_tc_trace, z, sizeof(z)); }
+    return 0;
+}
+#endif
