@@ -93,7 +93,7 @@ def build_reference_train(reference_root="/root/reference", verbose=False):
     with tempfile.TemporaryDirectory() as tmp:
         shutil.copy(src, os.path.join(tmp, "train.cpp"))
         cmd = ["g++", "-std=c++23", "-O2", "-I", HERE, "-I/usr/local/cuda/include", os.path.join(tmp, "train.cpp"), "-o", TRAIN_BIN,
-               "-L" + HERE, "-lgradc_b200", "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath," + HERE, "-Wl,-rpath,/usr/local/cuda/lib64"]
+               "-L" + HERE, "-lgradc_b200", "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath,/usr/local/cuda/lib64"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("train.cpp did not build against the host API:\n" + r.stderr[-6000:])

@@ -31,6 +31,7 @@ static int run_gemm(gcb_ctx* ctx, int op_a, int op_b, const GemmArgs& g, const c
             return GCB_UNSUPPORTED;
         }
         rc = gemm_simt_launch(ctx, ta, tb, g);
+        if (rc == GCB_OK && g.sm_probs) rc = softmax_bwd_apply_launch(ctx, g);  // this engine has no fused epilogue: same arithmetic as a second pass
     }
     if (e1) GCB_CHECK_CUDA(cudaEventRecord(e1, ctx->stream));
     return rc;
@@ -63,6 +64,19 @@ int gcb_gemm_batched_causal_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int
     GemmArgs g{M, N, K, alpha, beta, A, B, nullptr, C, lda, ldb, ldc, a_so, a_si, b_so, b_si, c_so, c_si, batch_outer, batch_inner};
     g.causal = causal;
     return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_batched_causal_f32");
+}
+
+int gcb_gemm_batched_softmax_bwd_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t K, float alpha, const float* A, int64_t lda, int64_t a_so, int64_t a_si, const float* B, int64_t ldb,
+                                     int64_t b_so, int64_t b_si, float* dscores, int64_t ldc, int64_t c_so, int64_t c_si, int64_t batch_outer, int64_t batch_inner, const float* probs,
+                                     const float* row_dot, float scale) {
+    GCB_REQUIRE(ctx, "gcb_gemm_batched_softmax_bwd_f32: ctx is NULL");
+    GCB_REQUIRE(batch_outer >= 0 && batch_inner >= 0, "gcb_gemm_batched_softmax_bwd_f32: negative batch count");
+    GCB_REQUIRE(M == 0 || batch_outer * batch_inner == 0 || (probs && row_dot), "gcb_gemm_batched_softmax_bwd_f32: NULL probs / row_dot");
+    GCB_REQUIRE(probs != dscores, "gcb_gemm_batched_softmax_bwd_f32: dscores must not alias probs");
+    GemmArgs g{M, M, K, alpha, 0.0f, A, B, nullptr, dscores, lda, ldb, ldc, a_so, a_si, b_so, b_si, c_so, c_si, batch_outer, batch_inner};
+    g.causal = 1;
+    g.sm_probs = probs; g.sm_rowdot = row_dot; g.sm_scale = scale;
+    return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_batched_softmax_bwd_f32");
 }
 
 int gcb_profile_gemm_begin(gcb_ctx* ctx) {

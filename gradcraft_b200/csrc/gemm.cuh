@@ -13,6 +13,11 @@ struct GemmArgs {
     int64_t a_so, a_si, b_so, b_si, c_so, c_si;  // batch strides (outer, inner) in elements
     int64_t batch_outer, batch_inner;
     int causal = 0;  // 0 none; 1 output needed on/below the diagonal only; 2 op(A)[m,k] = 0 for k > m; 3 op(A)[m,k] = 0 for k < m
+    // softmax-backward epilogue (needs causal == 1): C[m,n] = sm_scale * sm_probs[m,n] * (alpha * (op(A) op(B))[m,n] - sm_rowdot[m]) for n <= m, 0 for n > m.
+    // sm_probs is laid out like C; sm_rowdot holds M values per batch item, batch items in (outer, inner) order.
+    const float* sm_probs = nullptr;
+    const float* sm_rowdot = nullptr;
+    float sm_scale = 1.0f;
 };
 
 // fp32 FMA engine: any shape, any leading dimension.
@@ -21,5 +26,7 @@ int gemm_simt_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g);
 // to TMA: bases must be 16-byte aligned and every leading dimension / batch stride a multiple of 4 floats.
 int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g);
 bool gemm_tc_eligible(bool ta, bool tb, const GemmArgs& g);
+// C <- sm_scale * sm_probs * (C - sm_rowdot[row]) on/below the diagonal, 0 above: the softmax-backward epilogue as a pass of its own
+int softmax_bwd_apply_launch(gcb_ctx* ctx, const GemmArgs& g);
 
 }  // namespace gcb

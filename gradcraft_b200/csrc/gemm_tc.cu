@@ -46,6 +46,9 @@ struct TcParams {
     int split_mode;      // 1 (default): big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
                          // 0: big = rna_tf32(x) written back, small = x - big (does not rely on the hardware's truncation)
     float* partial;      // [splits][M][N] when splits > 1
+    const float* sm_probs;   // softmax-backward epilogue (see GemmArgs), or NULL
+    const float* sm_rowdot;
+    float sm_scale;
     int* status;
 };
 
@@ -365,17 +368,44 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
             const TileCoord tc = tile_coord(p, w, BN);
             if (tc.skip) continue;
             const uint32_t buf = lt & 1u;
-            ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float* cbase = to_partial ? p.partial + (int64_t)tc.split * p.M * p.N : p.C + (int64_t)tc.b_out * p.c_so + (int64_t)tc.b_in * p.c_si;
             const int64_t ld = to_partial ? p.N : p.ldc;
             const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
             const float* bias = to_partial ? nullptr : p.bias;
+            const float* sm_probs = (BN == 256 && !to_partial) ? p.sm_probs : nullptr;  // only the 256-wide instantiation carries this epilogue (the launcher sees to it)
+            const float* sm_rd = p.sm_rowdot + ((int64_t)tc.b_out * p.batch_inner + tc.b_in) * p.M;
+            // a triangular output is consumed in 128-wide diagonal blocks: columns right of this row tile's block are not written
+            const int64_t n_end = p.causal == 1 ? min(p.N, (int64_t)tc.m0 + TC_BM) : p.N;
+            if (sm_probs) {  // pull this warp's 32 rows of the probability tile into L2 while the MMAs of the tile are still running
+                const int64_t row0 = (int64_t)tc.m0 + 32 * q;
+                const int lines = (int)((min(n_end, (int64_t)tc.n0 + BN) - tc.n0 + 31) / 32);
+                for (int i = lane; i < 32 * lines; i += 32) {
+                    const int64_t r = row0 + i / lines;
+                    if (r < p.M) asm volatile("prefetch.global.L2 [%0];" ::"l"(sm_probs + (cbase - p.C) + r * ld + tc.n0 + 32 * (i % lines)));
+                }
+            }
+            ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int64_t nb = (int64_t)tc.n0 + 32 * c;
-                if (nb >= p.N) break;  // warp-uniform
+                if (nb >= n_end) break;  // warp-uniform
+                const int64_t m_first = ((int64_t)tc.m0 + 32 * q) + sub_r, n = nb + sub_c;
+                const bool blk_fast = vec_ok && ((int64_t)tc.m0 + 32 * q) + 32 <= p.M && nb + 32 <= p.N;  // whole 32 x 32 block in bounds
+                const int64_t step = 4 * ld;
+                // softmax-backward epilogue: the block's probabilities and row terms are requested before the accumulator is read
+                float4 pr[8];
+                float rdv[8];
+                if (sm_probs && blk_fast) {
+                    const bool below = nb <= (int64_t)tc.m0 + 32 * q + 31;  // some column of the block is at or left of the diagonal
+                    const float* pp = sm_probs + (cbase - p.C) + m_first * ld + n;
+#pragma unroll
+                    for (int r4 = 0; r4 < 8; ++r4) {
+                        pr[r4] = below ? ld4(pp + r4 * step) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        rdv[r4] = __ldg(sm_rd + m_first + 4 * r4);
+                    }
+                }
                 float v[32];
                 tmem_ld32(tmem_base + buf * BN + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), v);
                 // transpose through shared memory so that a warp stores whole 128-byte row segments
@@ -383,18 +413,22 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                 for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(stg + lane * S::EPI_PITCH + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
                 __syncwarp();
                 {
-                    const int64_t m_first = ((int64_t)tc.m0 + 32 * q) + sub_r, n = nb + sub_c;
                     float* dst = cbase + m_first * ld + n;
                     const float* src = stg + sub_r * S::EPI_PITCH + sub_c;
-                    if (vec_ok && ((int64_t)tc.m0 + 32 * q) + 32 <= p.M && nb + 32 <= p.N) {  // whole 32 x 32 block in bounds: pointer-increment fast path
+                    if (blk_fast) {  // pointer-increment fast path
                         float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (bias) bb = bias_vec ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(bias[n], bias[n + 1], bias[n + 2], bias[n + 3]);
-                        const int64_t step = 4 * ld;
 #pragma unroll
                         for (int r4 = 0; r4 < 8; ++r4, dst += step, src += 4 * S::EPI_PITCH) {
                             float4 o = *reinterpret_cast<const float4*>(src);
                             o.x = fmaf(o.x, alpha, bb.x); o.y = fmaf(o.y, alpha, bb.y); o.z = fmaf(o.z, alpha, bb.z); o.w = fmaf(o.w, alpha, bb.w);
                             if (beta != 0.0f) { const float4 old = ld4(dst); o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y); o.z = fmaf(beta, old.z, o.z); o.w = fmaf(beta, old.w, o.w); }
+                            if (sm_probs) {  // dS = scale * P * (dP - rowdot), zero above the diagonal
+                                const int64_t m = m_first + 4 * r4;
+                                const float rd = rdv[r4], sc = p.sm_scale;
+                                o.x = n + 0 <= m ? sc * pr[r4].x * (o.x - rd) : 0.0f; o.y = n + 1 <= m ? sc * pr[r4].y * (o.y - rd) : 0.0f;
+                                o.z = n + 2 <= m ? sc * pr[r4].z * (o.z - rd) : 0.0f; o.w = n + 3 <= m ? sc * pr[r4].w * (o.w - rd) : 0.0f;
+                            }
                             st4(dst, o);
                         }
                     } else {
@@ -408,6 +442,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                                     float r = sp[u] * alpha;
                                     if (bias) r += bias[n + u];
                                     if (beta != 0.0f) r += beta * d[u];
+                                    if (sm_probs) r = n + u <= m ? p.sm_scale * sm_probs[(d - p.C) + u] * (r - sm_rd[m]) : 0.0f;
                                     d[u] = r;
                                 }
                             }
@@ -824,9 +859,9 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     if (!enc) return GCB_UNSUPPORTED;
     cudaSetDevice(ctx->device);
     const int64_t batches = g.batch_outer * g.batch_inner;
-    const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+    const int BN = (g.N > 128 || g.sm_probs) ? 256 : (g.N > 64 ? 128 : 64);
     static const int pair_env = [] { const char* e = getenv("GRADC_TC_PAIR"); return e ? atoi(e) : 1; }();
-    const bool use_pair = pair_env != 0 && BN == 256 && g.M > 128 && g.K >= 256;  // short K loops are epilogue-bound: nothing to gain from sharing B
+    const bool use_pair = pair_env != 0 && BN == 256 && g.M > 128 && g.K >= 256 && !g.sm_probs;  // short K loops are epilogue-bound: nothing to gain from sharing B
     CUtensorMap ma, mb;
     if (!encode_operand(enc, &ma, g.A, ta, g.M, g.K, g.lda, g.a_si, g.a_so, g.batch_inner, g.batch_outer, TC_BM)) return GCB_UNSUPPORTED;
     if (!encode_operand(enc, &mb, g.B, !tb, g.N, g.K, g.ldb, g.b_si, g.b_so, g.batch_inner, g.batch_outer, use_pair ? 128 : BN)) return GCB_UNSUPPORTED;
@@ -839,6 +874,7 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     p.tiles_m = use_pair ? (int)((g.M + 255) / 256) : (int)((g.M + TC_BM - 1) / TC_BM);
     p.k_blocks_total = (int)((g.K + TC_BK - 1) / TC_BK);
     p.status = ctx->d_status;
+    p.sm_probs = g.sm_probs; p.sm_rowdot = g.sm_rowdot; p.sm_scale = g.sm_scale;
     const int64_t tiles = (int64_t)p.tiles_n * p.tiles_m * batches;
     if (tiles > 2147483647LL / 2) return GCB_UNSUPPORTED;
     // split-K when the tiles alone would leave SMs idle: pick the slice count with the lowest modelled time

@@ -8,6 +8,7 @@
 // Cross-entropy forward: a persistent CTA streams a row twice (online max/sum, then normalise); the grid is
 // sized so that all rows in flight fit in L2 and the second pass does not go back to HBM.
 #include "common.cuh"
+#include "gemm.cuh"
 
 namespace gcb {
 
@@ -220,6 +221,58 @@ static int chunks_for(int64_t T) { return T <= 128 ? 1 : T <= 256 ? 2 : T <= 512
 
 using namespace gcb;
 
+// ---- pieces of the attention backward that fold the softmax backward into the dP GEMM --------------------------------------
+// sum_j dP[i,j] P[i,j] equals dO[i,:] . O[i,:] (P V = O), so the row term of the softmax backward is available before dP
+// exists and the GEMM that produces dP can apply the whole backward in its epilogue.
+// One group of LPR lanes per row: out[(bo * n_inner + bi) * rows + r] = sum_c a[row] * b[row], rows addressed through (outer, inner, row) strides.
+template <int LPR>
+__global__ void __launch_bounds__(256) rowdot_kernel(float* __restrict__ out, const float* __restrict__ a, int64_t lda, int64_t a_so, int64_t a_si, const float* __restrict__ b, int64_t ldb,
+                                                     int64_t b_so, int64_t b_si, int64_t rows, int cols, int64_t n_inner, int64_t total_rows, int vec_ok) {
+    const int sub = threadIdx.x % LPR;
+    const int64_t groups_per_block = blockDim.x / LPR;
+    for (int64_t base = (int64_t)blockIdx.x * groups_per_block; base < total_rows; base += (int64_t)gridDim.x * groups_per_block) {  // block-uniform trip count: the shuffles below need whole warps
+        const int64_t r = base + threadIdx.x / LPR;
+        const bool live = r < total_rows;
+        float acc = 0.0f;
+        if (live) {
+            const int64_t item = r / rows, row = r - item * rows, bo = item / n_inner, bi = item - bo * n_inner;
+            const float* pa = a + bo * a_so + bi * a_si + row * lda;
+            const float* pb = b + bo * b_so + bi * b_si + row * ldb;
+            if (vec_ok) {
+                for (int c = sub * 4; c < cols; c += LPR * 4) {
+                    const float4 x = ld4(pa + c), y = ld4(pb + c);
+                    acc = fmaf(x.x, y.x, fmaf(x.y, y.y, fmaf(x.z, y.z, fmaf(x.w, y.w, acc))));
+                }
+            } else {
+                for (int c = sub; c < cols; c += LPR) acc = fmaf(pa[c], pb[c], acc);
+            }
+        }
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (live && sub == 0) out[r] = acc;
+    }
+}
+
+// C <- scale * P * (C - rowdot[row]) on/below the diagonal, 0 above (the GEMM epilogue of the same name, as a pass of its own)
+__global__ void __launch_bounds__(256) softmax_bwd_apply_kernel(float* __restrict__ C, const float* __restrict__ P, const float* __restrict__ rowdot, float scale, int64_t M, int64_t N,
+                                                                int64_t ldc, int64_t c_so, int64_t c_si, int64_t n_inner, int64_t total) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i % N, rm = i / N, m = rm % M, item = rm / M, bo = item / n_inner, bi = item - bo * n_inner;
+        const int64_t off = bo * c_so + bi * c_si + m * ldc + n;
+        C[off] = n <= m ? scale * P[off] * (C[off] - rowdot[item * M + m]) : 0.0f;
+    }
+}
+
+namespace gcb {
+int softmax_bwd_apply_launch(gcb_ctx* ctx, const GemmArgs& g) {
+    const int64_t total = g.M * g.N * g.batch_outer * g.batch_inner;
+    if (total == 0) return GCB_OK;
+    softmax_bwd_apply_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)kSMs * 16), 256, 0, ctx->stream>>>(g.C, g.sm_probs, g.sm_rowdot, g.sm_scale, g.M, g.N, g.ldc, g.c_so, g.c_si,
+                                                                                                                  g.batch_inner, total);
+    return after_launch(ctx, "softmax_bwd_apply");
+}
+}  // namespace gcb
+
 extern "C" {
 
 static int csm_fwd(gcb_ctx* ctx, float* probs, const float* scores, float scale, int64_t rows, int64_t T, int band) {
@@ -268,6 +321,25 @@ int gcb_causal_softmax_bwd_f32(gcb_ctx* ctx, float* ds, const float* dp, const f
 int gcb_causal_softmax_bwd_band_f32(gcb_ctx* ctx, float* ds, const float* dp, const float* probs, float scale, int64_t rows, int64_t T, int accumulate, int band) {
     GCB_REQUIRE(band >= 0 && band % 4 == 0, "gcb_causal_softmax_bwd_band_f32: band must be a non-negative multiple of 4");
     return csm_bwd(ctx, ds, dp, probs, scale, rows, T, accumulate, band);
+}
+
+int gcb_rowdot_batched_f32(gcb_ctx* ctx, float* out, const float* a, int64_t lda, int64_t a_so, int64_t a_si, const float* b, int64_t ldb, int64_t b_so, int64_t b_si, int64_t rows, int64_t cols,
+                           int64_t batch_outer, int64_t batch_inner) {
+    GCB_REQUIRE(ctx && rows >= 0 && cols >= 0 && batch_outer >= 0 && batch_inner >= 0, "gcb_rowdot_batched_f32: bad arguments");
+    const int64_t total_rows = rows * batch_outer * batch_inner;
+    if (total_rows == 0) return GCB_OK;
+    GCB_REQUIRE(out && (cols == 0 || (a && b)), "gcb_rowdot_batched_f32: NULL operand");
+    GCB_REQUIRE(cols < (int64_t(1) << 30), "gcb_rowdot_batched_f32: rows too long");
+    cudaSetDevice(ctx->device);
+    auto ok4 = [](int64_t v) { return v % 4 == 0; };
+    const int vec_ok = cols % 4 == 0 && aligned16(a) && aligned16(b) && ok4(lda) && ok4(ldb) && ok4(a_so) && ok4(a_si) && ok4(b_so) && ok4(b_si);
+    const int lpr = cols <= 32 ? 8 : (cols <= 64 ? 16 : 32);
+    const int64_t groups = 256 / lpr;
+    const unsigned blocks = (unsigned)std::min<int64_t>((total_rows + groups - 1) / groups, (int64_t)kSMs * 16);
+#define GCB_L(L) rowdot_kernel<L><<<blocks, 256, 0, ctx->stream>>>(out, a, lda, a_so, a_si, b, ldb, b_so, b_si, rows, (int)cols, batch_inner, total_rows, vec_ok)
+    if (lpr == 8) GCB_L(8); else if (lpr == 16) GCB_L(16); else GCB_L(32);
+#undef GCB_L
+    return after_launch(ctx, "rowdot");
 }
 
 int gcb_softmax_ce_fwd_f32(gcb_ctx* ctx, float* loss, float* probs, const float* logits, const void* targets, int index_type, int64_t rows, int64_t V, float eps) {

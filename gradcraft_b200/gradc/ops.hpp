@@ -610,7 +610,8 @@ class SDPANode : public Node<float> {
     Tensor<float> m_q, m_k, m_v;
     float m_scale;
     int64_t m_B, m_H, m_T, m_D;
-    Tensor<float> m_probs;
+    Tensor<float> m_probs;  // kept for backward
+    std::shared_ptr<Storage<float>> m_out_storage;  // O, for the row term dO . O of the softmax backward: the storage object of the tensor this node creates (realize() hands it the data)
 
     static void strides4(const Tensor<float>& t, int64_t& so, int64_t& si, int64_t& ld) { so = t.strides()[0]; si = t.strides()[1]; ld = t.strides()[2]; }
 
@@ -649,9 +650,12 @@ public:
             push_grad(m_v, dv);
         }
         if (m_q.requires_grad() || m_k.requires_grad()) {
-            Tensor<float> ds({B * H, T, T}, g.device(), uninitialized);  // dP = dO . V^T, then dS in place
-            gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_T, T, T, D, 1.0f, g.data_ptr(), gl, go, gi, m_v.data_ptr(), vl, vo, vi, 0.0f, ds.data_ptr(), T, H * T * T, T * T, B, H, 1), "attention dP");
-            gcb_check(gcb_causal_softmax_bwd_band_f32(c, ds.data_ptr(), ds.data_ptr(), m_probs.data_ptr(), m_scale, B * H * T, T, 0, kCausalBand), "causal softmax backward");
+            // dS = scale * P * (dO . V^T - rowdot), rowdot = sum_j dP_ij P_ij = dO_i . O_i: the softmax backward runs in the epilogue of the dP GEMM
+            Tensor<float> ds({B * H, T, T}, g.device(), uninitialized);
+            Tensor<float> rowdot({B * H * T}, g.device(), uninitialized);
+            gcb_check(gcb_rowdot_batched_f32(c, rowdot.data_ptr(), g.data_ptr(), gl, go, gi, m_out_storage->data(), H * D, T * H * D, D, T, D, B, H), "attention dO . O");
+            gcb_check(gcb_gemm_batched_softmax_bwd_f32(c, GCB_OP_N, GCB_OP_T, T, D, 1.0f, g.data_ptr(), gl, go, gi, m_v.data_ptr(), vl, vo, vi, ds.data_ptr(), T, H * T * T, T * T, B, H, m_probs.data_ptr(),
+                                                       rowdot.data_ptr(), m_scale), "attention dS");
             if (m_q.requires_grad()) {  // dQ = dS . K
                 Tensor<float> dq = fresh();
                 gcb_check(gcb_gemm_batched_causal_f32(c, GCB_OP_N, GCB_OP_N, T, D, T, 1.0f, ds.data_ptr(), T, H * T * T, T * T, m_k.data_ptr(), kl, ko, ki, 0.0f, dq.data_ptr(), H * D, T * H * D, D, B, H, 2), "attention dQ");
@@ -663,9 +667,10 @@ public:
                 push_grad(m_k, dk);
             }
         }
-        if (!retain_graph) m_probs = Tensor<float>();
+        if (!retain_graph) { m_probs = Tensor<float>(); m_out_storage.reset(); }
     }
     std::vector<TensorStateBase*> get_input_states() override { return {m_q._get_state_base(), m_k._get_state_base(), m_v._get_state_base()}; }
+    void set_output_storage(std::shared_ptr<Storage<float>> s) { m_out_storage = std::move(s); }
 };
 
 inline Tensor<float> sdpa(Tensor<float> q, Tensor<float> k, Tensor<float> v, bool is_causal = false, std::optional<Tensor<float>> /*custom_mask*/ = std::nullopt,
@@ -680,7 +685,9 @@ inline Tensor<float> sdpa(Tensor<float> q, Tensor<float> k, Tensor<float> v, boo
     const float s = scale.value_or(static_cast<float>(1.0 / std::sqrt((double)D)));
     Tensor<float> out({B, H, T, D}, q.requires_grad() || k.requires_grad() || v.requires_grad(), lazy, d);
     out.m_strides = SDPANode::out_strides(H, T, D);
-    out._get_state()->m_creation_op = std::make_unique<SDPANode>(std::move(q), std::move(k), std::move(v), s);
+    auto node = std::make_unique<SDPANode>(std::move(q), std::move(k), std::move(v), s);
+    node->set_output_storage(out._get_storage());
+    out._get_state()->m_creation_op = std::move(node);
     return out;
 }
 

@@ -143,6 +143,26 @@ GCB_API int gcb_gemm_batched_causal_f32(gcb_ctx* ctx, int op_a, int op_b, int64_
                                 float beta, float* C, int64_t ldc, int64_t c_stride_outer, int64_t c_stride_inner,
                                 int64_t batch_outer, int64_t batch_inner, int causal);
 
+/* Attention backward with the causal-softmax backward folded into the GEMM that produces dP
+ * (frontend/tensor_other.hpp:53-93 composes matmul and causal_softmax; cuda_math.hpp's apply_causal_softmax_backward is the
+ * pass this epilogue absorbs).  Per batch item, with dP = alpha * op(A) op(B) (M x M, K deep):
+ *   dscores[m, n] = scale * probs[m, n] * (dP[m, n] - row_dot[m])  for n <= m,   0 for n > m,
+ * written for every 128-row tile at or below the diagonal (columns up to the next multiple of 256; the rest is left
+ * untouched, as in gcb_gemm_batched_causal_f32 with causal = 1).  row_dot[m] must hold sum_n dP[m, n] * probs[m, n]; for
+ * attention that is dO[m, :] . O[m, :], which gcb_rowdot_batched_f32 computes without dP.  probs is laid out like
+ * dscores (ldc and batch strides); row_dot holds M floats per batch item, items in (outer, inner) order. */
+GCB_API int gcb_gemm_batched_softmax_bwd_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t K, float alpha,
+                                     const float* A, int64_t lda, int64_t a_stride_outer, int64_t a_stride_inner,
+                                     const float* B, int64_t ldb, int64_t b_stride_outer, int64_t b_stride_inner,
+                                     float* dscores, int64_t ldc, int64_t c_stride_outer, int64_t c_stride_inner,
+                                     int64_t batch_outer, int64_t batch_inner, const float* probs, const float* row_dot, float scale);
+
+/* out[(o * batch_inner + i) * rows + r] = sum_c a[o, i, r, c] * b[o, i, r, c]; rows of a and b are addressed through
+ * (outer, inner, row) strides in elements, columns are contiguous. */
+GCB_API int gcb_rowdot_batched_f32(gcb_ctx* ctx, float* out, const float* a, int64_t lda, int64_t a_stride_outer, int64_t a_stride_inner,
+                           const float* b, int64_t ldb, int64_t b_stride_outer, int64_t b_stride_inner,
+                           int64_t rows, int64_t cols, int64_t batch_outer, int64_t batch_inner);
+
 /* Measurement aid (the reference times with std::chrono around whole loops, benchmarks/bench_kernels.cpp:10-27):
  * between begin and end every GEMM launch is bracketed by CUDA events on the compute stream; end synchronises and
  * returns the number of launches, their summed device time and their algorithmic FLOPs (2*M*N*K*batches). */

@@ -140,3 +140,44 @@ def test_causal_batched_gemms_skip_only_known_zeros(env, engine):
         assert max_abs_rel(dV.cpu().numpy(), untok(p.transpose(0, 1, 3, 2) @ heads(q))) < TOL
     finally:
         ctx.ctx_set_gemm_engine(2)
+
+
+@pytest.mark.parametrize("engine", [2, 1])
+@pytest.mark.parametrize("T", [384, 200])
+def test_softmax_backward_in_the_dp_gemm_epilogue(env, engine, T):
+    """dS = scale * P * (dO V^T - dO . O) from one GEMM call equals the unfused chain dP GEMM -> causal-softmax backward."""
+    ctx, torch, capi = env
+    ctx.ctx_set_gemm_engine(engine)
+    try:
+        Bn, H, D = 2, 3, 64
+        C = H * D
+        scale = 0.125
+        q, k, v, do = rnd(30, Bn, T, C), rnd(31, Bn, T, C), rnd(32, Bn, T, C), rnd(33, Bn, T, C) * 1e-2
+        heads = lambda a: a.reshape(Bn, T, H, D).transpose(0, 2, 1, 3).astype(np.float64)
+        s = heads(q) @ heads(k).transpose(0, 1, 3, 2) * scale
+        s = np.where(np.tril(np.ones((T, T), bool)), s, -np.inf)
+        p = np.exp(s - s.max(-1, keepdims=True))
+        p /= p.sum(-1, keepdims=True)
+        o = p @ heads(v)
+        dp = heads(do) @ heads(v).transpose(0, 1, 3, 2)
+        ref = scale * p * (dp - (dp * p).sum(-1, keepdims=True))
+        P = torch.from_numpy(p.reshape(Bn * H, T, T).astype(np.float32)).cuda()
+        O = torch.from_numpy(o.transpose(0, 2, 1, 3).reshape(Bn, T, C).astype(np.float32)).cuda()
+        dO, Vd = torch.from_numpy(do).cuda(), torch.from_numpy(v).cuda()
+        rd = torch.empty(Bn * H * T, device="cuda")
+        ctx.rowdot_batched_f32(rd, dO, C, T * C, D, O, C, T * C, D, T, D, Bn, H)
+        ctx.sync()
+        want_rd = (heads(do) * o).sum(-1).reshape(-1)
+        assert max_abs_rel(rd.cpu().numpy(), want_rd) < 1e-6
+        dS = torch.full((Bn * H, T, T), float("nan"), device="cuda")
+        ctx.gemm_batched_softmax_bwd_f32(0, 1, T, D, 1.0, dO, C, T * C, D, Vd, C, T * C, D, dS, T, H * T * T, T * T, Bn, H, P, rd, scale)
+        ctx.sync()
+        got = dS.cpu().numpy().reshape(Bn, H, T, T)
+        low = np.tril(np.ones((T, T), bool))
+        assert np.isfinite(got[..., low]).all()
+        assert float(np.abs(got[..., low] - ref[..., low]).max() / np.abs(ref).max()) < 2e-5
+        # inside the 128-wide diagonal blocks everything above the diagonal is an explicit zero (the dQ / dK GEMMs read it)
+        blk = (np.arange(T)[:, None] // 128) == (np.arange(T)[None, :] // 128)
+        assert np.all(got[..., blk & ~low] == 0)
+    finally:
+        ctx.ctx_set_gemm_engine(2)
