@@ -240,6 +240,8 @@ def run_ours(args, rank, world, local_rank):
     else:
         ms_e2e, _, _, _, last_loss = timed(host, False, True, False)
     engine = lib.ctx_last_gemm_engine(ctx)
+    split_mode = lib.ctx_gemm_split_mode(ctx)
+    units = 4 if split_mode == 2 else 6  # tensor time per product in bf16-MMA units
     tokens_per_step = B * T * accum * world
     value = tokens_per_step * K / (ms_dev / 1e3)
     e2e = tokens_per_step * K / (ms_e2e / 1e3)
@@ -261,15 +263,16 @@ def run_ours(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic: Zipf(1.1) tokens (seed 1000+rank), N(0,0.02) weights (seed 0)",
             "config": {"workload": args.workload, "arch": arch, "layers": L, "d_model": C, "heads": H, "d_ff": F, "seq_len": T, "vocab": V, "batch_per_gpu": B, "micro_batches_per_step": accum,
                        "global_batch": B * accum * world, "params": nparams, "parallelism": "dp%d" % world, "gradient_buckets": nbuckets,
-                       "l2": "working set per step (%.1f GB arena high-water) far exceeds the 126 MB L2" % (hwm / 1e9), "gemm_engine": {1: "simt_fp32", 2: "tcgen05_3xtf32"}.get(engine, "none"),
+                       "l2": "working set per step (%.1f GB arena high-water) far exceeds the 126 MB L2" % (hwm / 1e9), "gemm_engine": {1: "simt_fp32", 2: "tcgen05_split_fp32(mode %d)" % split_mode}.get(engine, "none"),
                        "algorithmic_gflop_per_token": fpt / 1e9, "step_tflops": fpt * tokens_per_step / world / (ms_dev / K / 1e3) / 1e12},
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8 * accum, "d2h_bytes_per_step": 4 * accum, "ms_per_step": ms_e2e / K, "last_loss": last_loss},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tensor_tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tensor_tflops"],
                          "traffic": 238.5e6, "traffic_note": "dram read+write of one captured launch of the most frequent shape (M=32768, N=K=1024; algorithmic 272.6 MB, part of C still in L2): profiles/gemm_tc_kernel_linear_fwd_32768x1024x1024.md",
-                         "frac_of_3xtf32_ceiling": achieved / (pk["tensor_tflops"] / 6.0),
-                         "kernel": "gemm (%d launches, %.1f ms of the timed region)" % (n_gemm, gemm_ms), "peak_source": "%s dense bf16, sustained; 3xTF32 issues 3 tf32 MMAs per product, so its ceiling is 1/6 of this" % pk["source"],
+                         "frac_of_split_ceiling": achieved / (pk["tensor_tflops"] / units),
+                         "kernel": "gemm (%d launches, %.1f ms of the timed region)" % (n_gemm, gemm_ms),
+                         "peak_source": "%s dense bf16, sustained; split mode %d spends the tensor time of %d bf16 MMAs per product (a tf32 MMA counts 2), so its ceiling is 1/%d of this" % (pk["source"], split_mode, units, units),
                          "gemm_share_of_step": gemm_ms / ms_dev},
             "cpu_baseline": cpu,
         }
@@ -348,6 +351,7 @@ def run_gemm(args):
 
     ctx = capi.Context(0)
     pk = peaks()
+    units = 4 if ctx.ctx_gemm_split_mode() == 2 else 6  # tensor time per product in bf16-MMA units
     M, C, F, V, T, D, BH = 32768, 1024, 4096, 32768, 1024, 64, 512
     # name, opa, opb, M, N, K, batches (attention shapes are strided over (B, T, H*D) buffers exactly as the step runs them: causal
     # variants that skip known zeros; their TFLOP/s are quoted on the dense 2*M*N*K count, as the reference computes them)
@@ -390,12 +394,12 @@ def run_gemm(args):
             ts.append(s.elapsed_time(e))
         ms = float(np.median(ts))
         fl = 2.0 * m * n * k * nb
-        out[name] = {"ms": ms, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / pk["tensor_tflops_burst"], "frac_of_3xtf32_ceiling": fl / ms / 1e9 / (pk["tensor_tflops_burst"] / 6), "engine": ctx.ctx_last_gemm_engine()}
+        out[name] = {"ms": ms, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / pk["tensor_tflops_burst"], "frac_of_split_ceiling": fl / ms / 1e9 / (pk["tensor_tflops_burst"] / units), "engine": ctx.ctx_last_gemm_engine()}
         del fn
     ctx.sync()
     worst = min(out.values(), key=lambda d: d["tflops"])
     print(json.dumps({"metric": "GEMM engine, algorithmic TFLOP/s on the shapes of one gpt180m step", "value": worst["tflops"], "unit": "TFLOP/s (slowest shape)", "n_gpus": 1, "steps": max(3, args.steps),
-                      "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "f32 (3xTF32)", "data": "synthetic N(0,1)", "config": {"workload": "gemm", "l2": "operands of the large shapes exceed the 126 MB L2"},
+                      "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "f32 (split mode %d)" % ctx.ctx_gemm_split_mode(), "data": "synthetic N(0,1)", "config": {"workload": "gemm", "l2": "operands of the large shapes exceed the 126 MB L2"},
                       "peak_tflops": pk["tensor_tflops_burst"], "peak_source": pk["source"] + " dense bf16 burst", "shapes": out}))
     ctx.close()
 

@@ -72,7 +72,7 @@ class Lib:
             fn = getattr(self.cdll, name)  # AttributeError here means the header declares a symbol the library lacks
             fn.restype, fn.argtypes = restype, argtypes
             self.names.append(name)
-            checked = restype is ctypes.c_int and name not in ("gcb_ctx_device", "gcb_ctx_last_gemm_engine")
+            checked = restype is ctypes.c_int and name not in ("gcb_ctx_device", "gcb_ctx_last_gemm_engine", "gcb_ctx_gemm_split_mode")
             setattr(self, name[4:], self._wrap(fn, checked))
 
     def _wrap(self, fn, checked):

@@ -64,6 +64,7 @@ struct gcb_ctx {
     int64_t launches = 0;
     int gemm_engine = 0;       // 0 auto, 1 simt, 2 tcgen05
     int last_gemm_engine = 0;
+    int gemm_split_mode = 2;   // see gcb_ctx_set_gemm_split_mode
     int* d_status = nullptr;   // device-side status word written by kernels that give up on a bounded wait
     void* nccl_comm = nullptr;
     int dp_rank = 0, dp_world = 1;

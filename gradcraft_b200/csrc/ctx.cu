@@ -177,6 +177,7 @@ static int ctx_create_common(int device, void* stream, bool own, gcb_ctx** out) 
     GCB_CHECK_CUDA(cudaMalloc(&c->d_status, sizeof(int) * 4));
     GCB_CHECK_CUDA(cudaMemset(c->d_status, 0, sizeof(int) * 4));
     if (const char* g = getenv("GRADC_GEMM_ENGINE")) c->gemm_engine = atoi(g);
+    if (const char* g = getenv("GRADC_TC_SPLIT_MODE")) { const int m = atoi(g); if (m >= 0 && m <= 2) c->gemm_split_mode = m; }
     *out = c;
     return GCB_OK;
 }
@@ -210,6 +211,13 @@ int gcb_ctx_set_gemm_engine(gcb_ctx* ctx, int engine) {
     ctx->gemm_engine = engine;
     return GCB_OK;
 }
+
+int gcb_ctx_set_gemm_split_mode(gcb_ctx* ctx, int mode) {
+    GCB_REQUIRE(ctx && mode >= 0 && mode <= 2, "gcb_ctx_set_gemm_split_mode: mode must be 0, 1 or 2");
+    ctx->gemm_split_mode = mode;
+    return GCB_OK;
+}
+int gcb_ctx_gemm_split_mode(gcb_ctx* ctx) { return ctx ? ctx->gemm_split_mode : -1; }
 
 int gcb_ctx_sync(gcb_ctx* ctx) {
     GCB_REQUIRE(ctx, "gcb_ctx_sync: ctx is NULL");

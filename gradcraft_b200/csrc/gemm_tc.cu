@@ -1,20 +1,24 @@
-// tcgen05 / TMEM GEMM with fp32 accuracy through three TF32 products (3xTF32), operands staged by TMA.
+// tcgen05 / TMEM GEMM with fp32-class accuracy from split operands, staged by TMA.
 // Reference counterpart: cublasSgemm / cublasSgemmStridedBatched in TF32 tensor-op mode
 // (backend/cuda/kernels_math.cu:27-36, 725-779), which keeps only 10 mantissa bits of each operand.
 //
-// Persistent CTAs (one per SM) walk over 128 x BN tiles of C.  Warp roles:
-//   warp 0      TMA producer: per 16-wide K block, one bulk tensor copy per operand tile into a 4-stage smem ring
-//   warp 1      MMA issuer: allocates 2 x BN TMEM columns (double-buffered accumulator), issues tcgen05.mma.kind::tf32
-//   warps 2..5  splitter: big / small parts of every landed tile
+// Persistent CTAs walk over 128 x BN tiles of C (or CTA pairs over 256 x 256 tiles, second half of this file).  Warp roles:
+//   warp 0      TMA producer: per 16-wide K block, one bulk tensor copy per operand tile into a smem ring
+//   warp 1      MMA issuer: allocates 2 x BN TMEM columns (double-buffered accumulator), issues the tcgen05.mma sequence
+//   warps 2..5  splitter: derives the second-order parts of every landed tile into its twin tile
 //   warps 6..9  epilogue: TMEM -> registers -> smem transpose -> 128-byte row segments in global memory, overlapped with
 //               the main loop of the next tile
-// 3xTF32: the splitter rewrites each landed fp32 tile in place as `big` = x rounded to TF32 and writes `small` = x - big
-// (exact in fp32) to a twin tile; the issuer accumulates big*big + small*big + big*small into the same TMEM
-// accumulator, so the dropped term is small*small ~ 2^-22 of the product.
-// Shared-memory layouts are the canonical UMMA ones the TMA swizzle modes produce:
+// Split operands: every fp32 value is x = t + s, t = x truncated to TF32 (the tensor core reads t straight from the raw
+// tile: it ignores the 13 low mantissa bits) and s = x - t, exact.  The default mode accumulates
+//   t_a t_b (kind::tf32)  +  bf16(s_a) bf16(b)  +  bf16(a) bf16(s_b) (kind::f16, BF16 inputs, twice the TF32 rate)
+// into one TMEM accumulator: the dropped terms are ~2^-19 of a product.  Mode 1 issues three TF32 products instead
+// (t_a t_b + s_a t_b + t_a s_b, dropped term ~2^-22) at 1.5x the tensor time and 1.2x the shared-memory traffic; both
+// modes measure the same error against fp64 (~2e-6 of the result at K ~ 1000), which comes from the accumulator.
+// Shared-memory layouts.  Raw tiles are the canonical UMMA layouts the TMA swizzle modes produce:
 //   operand contiguous along K   -> rows of 64 B, SWIZZLE_64B, descriptor "K-major",  SBO = 512 B, +32 B per K=8 step
 //   operand contiguous along M/N -> 32-float chunks x 16 k-rows, 128-byte swizzle in 32-byte units (the only MN-major
 //                                   layout TF32 accepts), "MN-major", LBO = 2 KB (next chunk), SBO = 512 B (next 4 k-rows)
+// BF16 twin tiles are written by the splitter, always K-major and unswizzled (8 x 16-byte core matrices, LBO 128 B, SBO 256 B).
 // Every mbarrier wait is bounded; a wait that runs out sets the context's status word and the kernel drains and exits
 // (TMEM is always released), so a logic error cannot hang the device.
 // Split-K (deterministic): when a problem has too few tiles to fill 148 SMs, K is cut into slices whose partial tiles go
@@ -43,8 +47,9 @@ struct TcParams {
     int64_t loop_end;    // bound of the persistent loop: work_items, rounded up to whole rounds where the snake order needs it
     int kept_per_batch;  // causal mode 1: tiles per batch at or below the diagonal
     int causal;          // see GemmArgs::causal
-    int split_mode;      // 1 (default): big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
-                         // 0: big = rna_tf32(x) written back, small = x - big (does not rely on the hardware's truncation)
+    int split_mode;      // 2 (default): one TF32 product of the truncated parts + two BF16 cross products (split_hybrid below);
+                         // 1: three TF32 products; big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
+                         // 0: as 1 with big = rna_tf32(x) written back, small = x - big (does not rely on the hardware's truncation)
     float* partial;      // [splits][M][N] when splits > 1
     const float* sm_probs;   // softmax-backward epilogue (see GemmArgs), or NULL
     const float* sm_rowdot;
@@ -109,6 +114,61 @@ __device__ __forceinline__ float round_tf32(float x) {  // nearest TF32 value, r
 }
 
 __device__ __forceinline__ float trunc_tf32(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {  // two round-to-nearest bf16 values, `lo` at the lower address
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Split mode 2 ("TF32 + 2 x BF16"): x = t + s with t = x truncated to TF32 (what the tensor core reads from the raw tile) and
+// s = x - t (exact).  a b ~ t_a t_b (one TF32 product) + bf16(s_a) bf16(b) + bf16(a) bf16(s_b) (two BF16 products at twice
+// the TF32 rate): two thirds of the tensor time of three TF32 products, error ~ 2^-19 of a product instead of 2^-22,
+// full fp32 exponent range.  The BF16 operands go to the twin tile of each operand (same bytes as an fp32 `small` tile):
+// bf16(x) in its first half, bf16(s) in the second, both K-major without swizzle — 8-row x 16-byte core matrices,
+// 128 B apart along K (LBO), 256 B apart along M / N (SBO) — whatever the raw tile's orientation.
+// ROWS = rows of the operand tile (its M or N extent).  t = thread index among the 128 splitter threads.
+template <bool MN, int ROWS>
+__device__ __forceinline__ void split_hybrid(const uint8_t* raw, uint8_t* twin, int t) {
+    uint8_t* big = twin;
+    uint8_t* sml = twin + ROWS * 32;
+    if (!MN) {
+        // raw: ROWS rows of 64 B (16 k), 16-byte chunk index XOR ((row >> 1) & 3)  [64-byte swizzle]
+        float4 x[ROWS / 32];
+#pragma unroll
+        for (int v = 0; v < ROWS / 32; ++v) x[v] = reinterpret_cast<const float4*>(raw)[t + 128 * v];
+#pragma unroll
+        for (int v = 0; v < ROWS / 32; ++v) {
+            const int idx = t + 128 * v, row = idx >> 2, lc = (idx & 3) ^ ((row >> 1) & 3);  // lc: logical chunk = k / 4
+            const uint32_t off = (uint32_t)(row >> 3) * 256u + (uint32_t)(lc >> 1) * 128u + (uint32_t)(row & 7) * 16u + (uint32_t)(lc & 1) * 8u;
+            const float4 s = make_float4(x[v].x - trunc_tf32(x[v].x), x[v].y - trunc_tf32(x[v].y), x[v].z - trunc_tf32(x[v].z), x[v].w - trunc_tf32(x[v].w));
+            *reinterpret_cast<uint2*>(big + off) = make_uint2(pack_bf16(x[v].x, x[v].y), pack_bf16(x[v].z, x[v].w));
+            *reinterpret_cast<uint2*>(sml + off) = make_uint2(pack_bf16(s.x, s.y), pack_bf16(s.z, s.w));
+        }
+    } else {
+        // raw: ROWS / 32 boxes of 16 k-rows x 32 floats (128 B rows), 32-byte unit index XOR (k & 3)  [128-byte swizzle in 32-byte units]
+#pragma unroll
+        for (int mn = t; mn < ROWS; mn += 128) {
+            const uint8_t* box = raw + (mn >> 5) * 2048;
+            const int j = mn & 31;
+            float x[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) x[k] = *reinterpret_cast<const float*>(box + k * 128 + ((((j >> 3) ^ (k & 3)) << 5) | ((j & 7) << 2)));
+            const uint32_t off = (uint32_t)(mn >> 3) * 256u + (uint32_t)(mn & 7) * 16u;
+#pragma unroll
+            for (int kc = 0; kc < 2; ++kc) {
+                const float* y = x + 8 * kc;
+                float s[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[e] = y[e] - trunc_tf32(y[e]);
+                *reinterpret_cast<uint4*>(big + off + kc * 128) = make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]), pack_bf16(y[6], y[7]));
+                *reinterpret_cast<uint4*>(sml + off + kc * 128) = make_uint4(pack_bf16(s[0], s[1]), pack_bf16(s[2], s[3]), pack_bf16(s[4], s[5]), pack_bf16(s[6], s[7]));
+            }
+        }
+    }
+}
 
 // Optional role timing (compile with -DGCB_TC_TRACE): per role, cycles spent waiting on barriers and cycles in total,
 // summed over CTAs into g_tc_trace[2 * role], [2 * role + 1]; roles: 0 producer, 1 issuer, 2 splitter warps, 3 epilogue warps.
@@ -275,6 +335,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
         if (lane == 0) {
             // instruction descriptor: fp32 accumulate, TF32 x TF32, operand majors, N >> 3, M >> 4
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            const uint32_t idesc_bf = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);  // BF16 x BF16, both K-major
             uint32_t it = 0, lt = 0;
             bool ok = true;
             TR_BEGIN(1);
@@ -301,9 +362,18 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                         const uint64_t a_sml = A_MN ? make_desc(sa + S::A_BYTES + a_off, 2048, 512, 1) : make_desc(sa + S::A_BYTES + a_off, 16, 512, 4);
                         const uint64_t b_big = B_MN ? make_desc(sb + b_off, 2048, 512, 1) : make_desc(sb + b_off, 16, 512, 4);
                         const uint64_t b_sml = B_MN ? make_desc(sb + S::B_BYTES + b_off, 2048, 512, 1) : make_desc(sb + S::B_BYTES + b_off, 16, 512, 4);
-                        umma_tf32(d_tmem, a_sml, b_big, idesc, (i | j) ? 1u : 0u);  // small terms first: they are added to a small running sum
-                        umma_tf32(d_tmem, a_big, b_sml, idesc, 1u);
-                        umma_tf32(d_tmem, a_big, b_big, idesc, 1u);
+                        if (p.split_mode == 2) {
+                            umma_tf32(d_tmem, a_big, b_big, idesc, (i | j) ? 1u : 0u);
+                        } else {
+                            umma_tf32(d_tmem, a_sml, b_big, idesc, (i | j) ? 1u : 0u);  // small terms first: they are added to a small running sum
+                            umma_tf32(d_tmem, a_big, b_sml, idesc, 1u);
+                            umma_tf32(d_tmem, a_big, b_big, idesc, 1u);
+                        }
+                    }
+                    if (p.split_mode == 2) {  // the two cross terms in BF16, one K = 16 instruction each
+                        const uint32_t ta = sa + S::A_BYTES, tb = sb + S::B_BYTES;  // twin tiles: bf16(x) then bf16(x - trunc(x))
+                        umma_bf16(d_tmem, make_desc(ta + S::A_BYTES / 2, 128, 256, 0), make_desc(tb, 128, 256, 0), idesc_bf, 1u);
+                        umma_bf16(d_tmem, make_desc(ta, 128, 256, 0), make_desc(tb + S::B_BYTES / 2, 128, 256, 0), idesc_bf, 1u);
                     }
                     umma_commit(empty_bar(s));  // the stage may be refilled once these MMAs have read it
                 }
@@ -345,8 +415,14 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                         }
                     }
                 };
-                split_tile(stage, S::A_BYTES / 16, S::A_BYTES / 16);
-                split_tile(stage + 2 * (S::A_BYTES / 16), S::B_BYTES / 16, S::B_BYTES / 16);
+                if (p.split_mode == 2) {
+                    uint8_t* st = gen_base + s * S::STAGE_BYTES;
+                    split_hybrid<A_MN, TC_BM>(st, st + S::A_BYTES, t);
+                    split_hybrid<B_MN, BN>(st + 2 * S::A_BYTES, st + 2 * S::A_BYTES + S::B_BYTES, t);
+                } else {
+                    split_tile(stage, S::A_BYTES / 16, S::A_BYTES / 16);
+                    split_tile(stage + 2 * (S::A_BYTES / 16), S::B_BYTES / 16, S::B_BYTES / 16);
+                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(conv_bar(s));
@@ -485,6 +561,9 @@ __device__ __forceinline__ void mbar_arrive_on_cta(uint32_t local_bar, uint32_t 
 __device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {  // arrives on the barrier at this offset in both CTAs of the pair
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
@@ -563,6 +642,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            TR_BEGIN(0);
             for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
                 const TileCoord tc = pair_tile_coord(p, w);
                 if (tc.skip) continue;
@@ -570,7 +650,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
                 for (int i = 0; i < tc.nkb; ++i, ++it) {
                     const int s = it % NST;
                     const uint32_t ph = (it / NST) & 1u;
-                    ok = mbar_wait(empty_bar(s), ph ^ 1u, p.status, 11);
+                    ok = TR_WAIT(mbar_wait(empty_bar(s), ph ^ 1u, p.status, 11));
                     if (!ok) break;
                     const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
                     mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES);
@@ -589,13 +669,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
                     }
                 }
             }
+            TR_END();
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer: the leader CTA only ----------------
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            const uint32_t idesc_bf = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);  // BF16 x BF16, both K-major
             uint32_t it = 0, lt = 0;
             bool ok = true;
+            TR_BEGIN(1);
             for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
                 const TileCoord tc = pair_tile_coord(p, w);
                 if (tc.skip) continue;
@@ -607,7 +690,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
                 for (int i = 0; i < tc.nkb; ++i, ++it) {
                     const int s = it % NST;
                     const uint32_t ph = (it / NST) & 1u;
-                    ok = mbar_wait(conv_bar(s), ph, p.status, 12);  // both CTAs' tiles landed and were split
+                    ok = TR_WAIT(mbar_wait(conv_bar(s), ph, p.status, 12));  // both CTAs' tiles landed and were split
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
@@ -618,28 +701,39 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
                         const uint64_t a_sml = A_MN ? make_desc(sa + S::A_BYTES + a_off, 2048, 512, 1) : make_desc(sa + S::A_BYTES + a_off, 16, 512, 4);
                         const uint64_t b_big = B_MN ? make_desc(sb + b_off, 2048, 512, 1) : make_desc(sb + b_off, 16, 512, 4);
                         const uint64_t b_sml = B_MN ? make_desc(sb + S::B_BYTES + b_off, 2048, 512, 1) : make_desc(sb + S::B_BYTES + b_off, 16, 512, 4);
-                        umma_tf32_pair(d_tmem, a_sml, b_big, idesc, (i | j) ? 1u : 0u);
-                        umma_tf32_pair(d_tmem, a_big, b_sml, idesc, 1u);
-                        umma_tf32_pair(d_tmem, a_big, b_big, idesc, 1u);
+                        if (p.split_mode == 2) {
+                            umma_tf32_pair(d_tmem, a_big, b_big, idesc, (i | j) ? 1u : 0u);
+                        } else {
+                            umma_tf32_pair(d_tmem, a_sml, b_big, idesc, (i | j) ? 1u : 0u);
+                            umma_tf32_pair(d_tmem, a_big, b_sml, idesc, 1u);
+                            umma_tf32_pair(d_tmem, a_big, b_big, idesc, 1u);
+                        }
+                    }
+                    if (p.split_mode == 2) {
+                        const uint32_t ta = sa + S::A_BYTES, tb = sb + S::B_BYTES;
+                        umma_bf16_pair(d_tmem, make_desc(ta + S::A_BYTES / 2, 128, 256, 0), make_desc(tb, 128, 256, 0), idesc_bf, 1u);
+                        umma_bf16_pair(d_tmem, make_desc(ta, 128, 256, 0), make_desc(tb + S::B_BYTES / 2, 128, 256, 0), idesc_bf, 1u);
                     }
                     umma_commit_pair(empty_bar(s));
                 }
                 if (ok) umma_commit_pair(acc_full_bar(buf));
                 ++lt;
             }
+            TR_END();
         }
     } else if (warp < 6) {
         // ---------------- splitter (own A rows, own half of B) ----------------
         const int t = threadIdx.x - 64;
         uint32_t it = 0;
         bool ok = true;
+        TR_BEGIN(2);
         for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
             const TileCoord tc = pair_tile_coord(p, w);
             if (tc.skip) continue;
             for (int i = 0; i < tc.nkb; ++i, ++it) {
                 const int s = it % NST;
                 const uint32_t ph = (it / NST) & 1u;
-                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, 13)) != 0;
+                ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, p.status, 13)) != 0);
                 if (!ok) break;
                 float4* stage = reinterpret_cast<float4*>(gen_base + s * S::STAGE_BYTES);
                 auto split_tile = [&](float4* big, int n_vec) {
@@ -649,13 +743,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
                         big[t + 128 * q + n_vec] = make_float4(round_tf32(x.x - trunc_tf32(x.x)), round_tf32(x.y - trunc_tf32(x.y)), round_tf32(x.z - trunc_tf32(x.z)), round_tf32(x.w - trunc_tf32(x.w)));
                     }
                 };
-                split_tile(stage, S::A_BYTES / 16);
-                split_tile(stage + 2 * (S::A_BYTES / 16), S::B_BYTES / 16);
+                if (p.split_mode == 2) {
+                    uint8_t* st = gen_base + s * S::STAGE_BYTES;
+                    split_hybrid<A_MN, TC_BM>(st, st + S::A_BYTES, t);
+                    split_hybrid<B_MN, BN / 2>(st + 2 * S::A_BYTES, st + 2 * S::A_BYTES + S::B_BYTES, t);
+                } else {
+                    split_tile(stage, S::A_BYTES / 16);
+                    split_tile(stage + 2 * (S::A_BYTES / 16), S::B_BYTES / 16);
+                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive_on_cta(conv_bar(s), 0);  // the leader's barrier counts both CTAs' splitter warps
             }
         }
+        TR_END();
     } else {
         // ---------------- epilogue: this CTA's 128 rows of the pair tile ----------------
         const int q = warp & 3;
@@ -908,8 +1009,7 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
         for (int i = 0; i < p.tiles_m; ++i) p.kept_per_batch += causal_kept_cols(i, p.tiles_n, BN);
         p.work_items = (int64_t)p.kept_per_batch * batches;
     }
-    static const int split_mode_env = [] { const char* e = getenv("GRADC_TC_SPLIT_MODE"); return e ? atoi(e) : 1; }();
-    p.split_mode = split_mode_env;
+    p.split_mode = ctx->gemm_split_mode;
     dim3 grid((unsigned)std::min<int64_t>(p.work_items, (int64_t)kSMs * (BN == 64 ? 2 : 1)), 1, 1);
     p.loop_end = g.causal >= 2 ? (p.work_items + grid.x - 1) / grid.x * grid.x : p.work_items;  // snake order: whole rounds
     int rc;

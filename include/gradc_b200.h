@@ -62,10 +62,20 @@ GCB_API int gcb_ctx_device(gcb_ctx* ctx);
 GCB_API int gcb_ctx_sync(gcb_ctx* ctx); /* cudaStreamSynchronize + sticky-error check */
 /* Number of kernels this library launched through ctx since creation. */
 GCB_API int64_t gcb_ctx_launch_count(gcb_ctx* ctx);
-/* Which GEMM engine ran last: 0 none, 1 SIMT fp32, 2 tcgen05 3xTF32. */
+/* Which GEMM engine ran last: 0 none, 1 SIMT fp32, 2 tcgen05 (split fp32). */
 GCB_API int gcb_ctx_last_gemm_engine(gcb_ctx* ctx);
 /* Force the GEMM engine: 0 auto, 1 SIMT fp32 only, 2 tcgen05 only (fails where it cannot run). */
 GCB_API int gcb_ctx_set_gemm_engine(gcb_ctx* ctx, int engine);
+/* How the tcgen05 engine reaches fp32-class accuracy (cublasSgemm's TF32 mode in the reference, kernels_math.cu:27-36,
+ * keeps 10 mantissa bits and nothing else).  With x = t + s, t = x truncated to TF32, s = x - t:
+ *   2 (default)  a b ~ t_a t_b in TF32 + bf16(s_a) bf16(b) + bf16(a) bf16(s_b) in BF16: error ~2^-19 of a product
+ *   1            three TF32 products t_a t_b + s_a t_b + t_a s_b:                        error ~2^-22 of a product
+ *   0            as 1, with t rounded to nearest instead of truncated
+ * In all modes the fp32 accumulation of the tensor core (truncating adds) contributes about 2e-6 of the result at
+ * K ~ 1000, which is what the measured error of modes 1 and 2 alike comes to.  The environment variable
+ * GRADC_TC_SPLIT_MODE sets the initial value of new contexts. */
+GCB_API int gcb_ctx_set_gemm_split_mode(gcb_ctx* ctx, int mode);
+GCB_API int gcb_ctx_gemm_split_mode(gcb_ctx* ctx);
 
 /* ---- arena: CUDAMemPool::{allocate,free,clear,get_hwm_gb}, memory_pool.hpp:40-102 -------------- */
 GCB_API int gcb_arena_alloc(gcb_ctx* ctx, size_t bytes, void** out);

@@ -1,6 +1,8 @@
-"""The tcgen05 3xTF32 GEMM engine against float64 numpy: every operand layout, tile width, ragged edges, bias / beta
+"""The tcgen05 split-fp32 GEMM engine against float64 numpy: every operand layout, tile width, ragged edges, bias / beta
 epilogues, head-strided batches and split-K.  Tolerance: max-abs-rel 2e-5 per output (fp32-class accuracy; plain TF32
 would sit near 1e-3)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -52,19 +54,48 @@ def test_tc_gemm_vs_numpy(env, opa, opb, M, N, K):
     assert max_abs_rel(C.cpu().numpy(), 0.5 * (a @ b) + C0 + bias) < TOL
 
 
-def test_tc_gemm_is_fp32_class_not_tf32_class(env):
-    """Operands 1 + 1e-3 z: rounding them to TF32 once would cost ~4e-5 of the result here; the split engine must stay an
-    order of magnitude below that.  (Its residual error is the tensor core's truncating fp32 accumulation: a bias of a few
-    1e-6 on all-positive sums, measured 5e-6 at K = 256 and 2e-5 at K = 32768.)"""
+@pytest.mark.parametrize("mode", [2, 1, 0])
+def test_tc_gemm_is_fp32_class_not_tf32_class(env, mode):
+    """Operands 1 + 1e-3 z: rounding them to TF32 once would cost ~4e-5 of the result here; every split mode must stay an
+    order of magnitude below that.  (The residual error is the tensor core's truncating fp32 accumulation: a bias of a few
+    1e-6 on all-positive sums, measured 5e-6 at K = 256 and 2e-5 at K = 32768, the same for the TF32 + 2 x BF16 split and
+    for three TF32 products.)"""
     ctx, torch, capi = env
     M = N = K = 256
     A = (1.0 + rnd(5, M, K) * 1e-3).astype(np.float32)
     B = (1.0 + rnd(6, K, N) * 1e-3).astype(np.float32)
     C = torch.empty(M, N, device="cuda")
-    ctx.gemm_f32(0, 0, M, N, K, 1.0, torch.from_numpy(A).cuda(), K, torch.from_numpy(B).cuda(), N, 0.0, C, N, None)
-    ctx.sync()
+    default = ctx.ctx_gemm_split_mode()
+    assert default == int(os.environ.get("GRADC_TC_SPLIT_MODE", "2"))
+    ctx.ctx_set_gemm_split_mode(mode)
+    try:
+        ctx.gemm_f32(0, 0, M, N, K, 1.0, torch.from_numpy(A).cuda(), K, torch.from_numpy(B).cuda(), N, 0.0, C, N, None)
+        ctx.sync()
+    finally:
+        ctx.ctx_set_gemm_split_mode(default)
     ref = A.astype(np.float64) @ B.astype(np.float64)
     assert float(np.abs(C.cpu().numpy() - ref).max() / np.abs(ref).max()) < 1e-5
+
+
+@pytest.mark.parametrize("opa,opb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_split_modes_agree_on_zero_mean_operands(env, opa, opb):
+    """N(0,1) operands in every storage orientation (the splitter reads K-major and MN-major raw tiles differently), a shape
+    that runs the CTA-pair kernel and one that runs the single-CTA kernel: both split modes within 5e-6 of fp64."""
+    ctx, torch, capi = env
+    default = ctx.ctx_gemm_split_mode()
+    try:
+        for (M, N, K) in [(512, 512, 512), (256, 192, 80)]:
+            A = rnd(40, *((K, M) if opa else (M, K)))
+            B = rnd(41, *((N, K) if opb else (K, N)))
+            ref = (A.T if opa else A).astype(np.float64) @ (B.T if opb else B).astype(np.float64)
+            for mode in (2, 1):
+                ctx.ctx_set_gemm_split_mode(mode)
+                C = torch.empty(M, N, device="cuda")
+                ctx.gemm_f32(opa, opb, M, N, K, 1.0, torch.from_numpy(A).cuda(), A.shape[1], torch.from_numpy(B).cuda(), B.shape[1], 0.0, C, N, None)
+                ctx.sync()
+                assert max_abs_rel(C.cpu().numpy(), ref) < 5e-6, (mode, M, N, K)
+    finally:
+        ctx.ctx_set_gemm_split_mode(default)
 
 
 def test_tc_gemm_head_strided_batches(env):
