@@ -125,6 +125,35 @@ def reference_cpu_run(workload, steps, warmup, sample_B=1):
     return tok_s, cores, desc, "reference"
 
 
+def run_reference_cuda_arm(args, rank):
+    """The reference's own CUDA path (its .cu files built for sm_100a by oracle/build_ref.sh) on one GPU: the figure the
+    "x times the reference's CUDA path" target is quoted against.  Not the contract's reference arm (that is the CPU path)."""
+    if rank != 0:
+        return
+    arch, V, T, C, H, L, F, B, accum = WORKLOADS[args.workload]
+    harness = os.path.join(ROOT, "oracle", "_ref", "ref_harness_cuda")
+    if not os.path.exists(harness):
+        print(json.dumps({"impl": "reference-cuda", "unavailable": "oracle/_ref/ref_harness_cuda is not built"}))
+        return
+    from gradcraft_b200 import synth
+
+    Bs = args.ref_batch or B
+    with tempfile.TemporaryDirectory() as tmp:
+        synth.token_batches(99, 1, Bs, T, V).tofile(os.path.join(tmp, "tok.i64"))
+        cmd = [harness, "gptcuda", arch] + [str(v) for v in (V, T, C, H, L, F, Bs, args.steps, args.warmup)] + [os.path.join(tmp, "tok.i64")]
+        t0 = time.time()
+        r = subprocess.run(cmd, capture_output=True, text=True)
+    out = [l for l in r.stdout.splitlines() if l.startswith("tokens_per_s")]
+    if r.returncode != 0 or not out:
+        print(json.dumps({"impl": "reference-cuda", "unavailable": "ref_harness_cuda failed: " + ((r.stderr.strip().splitlines() or r.stdout.strip().splitlines() or ["?"])[-1])[:300]}))
+        return
+    f = out[-1].split()
+    print(json.dumps({"impl": "reference-cuda", "metric": "GPT fp32 train tokens/s (fwd+bwd+AdamW)", "value": float(f[1]), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": float(f[3]), "higher_is_better": True, "dtype": "f32 (cuBLAS TF32 tensor-op mode, as the reference sets it)", "data": "synthetic Zipf(1.1) tokens, one fixed batch",
+                      "config": {"workload": args.workload, "arch": arch, "layers": L, "d_model": C, "heads": H, "d_ff": F, "seq_len": T, "vocab": V, "batch": Bs},
+                      "pool_high_water_gb": float(f[5]), "last_loss": float(f[7]), "wall_s": time.time() - t0}))
+
+
 def run_reference_arm(args, rank):
     if rank != 0:
         return
@@ -409,13 +438,17 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
+    ap.add_argument("--ref-batch", type=int, default=0, help="sequences per step for --impl reference-cuda (default: the workload's)")
     ap.add_argument("--workload", default="gpt180m", choices=list(WORKLOADS) + ["kernels", "gemm"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
     ap.add_argument("--only", default="", help="gemm workload: run only the shapes whose name contains this text")
     args = ap.parse_args()
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference-cuda":
+        run_reference_cuda_arm(args, int(os.environ.get("RANK", "0")))
+        return
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return

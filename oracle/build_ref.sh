@@ -102,3 +102,31 @@ else
   echo "naive" > "$OUT/blas_kind.txt"
 fi
 echo "build_ref: wrote $OUT/ref_harness"
+
+# --- the reference's CUDA path (its two .cu files, nvcc for sm_100a, the flags of its own CMakeLists.txt:40) -------------
+# A fifth portability patch, for nvcc on LP64: atomicMax / atomicMin have no `long*` overload, so the int64 instantiation
+# of the reduction functors casts to `long long*` (same width, same operation).  Skipped when nvcc is absent.
+NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
+if [ -x "$NVCC" ] && [ "${REF_SKIP_CUDA:-0}" != "1" ]; then
+  python3 - "$G/backend/cuda/math_functors.cuh" <<'PY'
+import sys
+p = sys.argv[1]
+s = open(p).read()
+s = s.replace("atomicMax(adress, val);", "if constexpr (sizeof(T) == 8) atomicMax((long long*)adress, (long long)val); else atomicMax(adress, val);")
+s = s.replace("atomicMin(adress, val);", "if constexpr (sizeof(T) == 8) atomicMin((long long*)adress, (long long)val); else atomicMin(adress, val);")
+open(p, "w").write(s)
+PY
+  # the .cu files see lobotomized_broadcast_view() only through the friend declaration that patch 2 removes: pre-include its header
+  NVFLAGS="-std=c++20 -gencode arch=compute_100a,code=sm_100a -O3 -use_fast_math -w -I$SCRATCH/shim -I$SCRATCH/ref -include $G/core/detail/tensor_lob_view.hpp"
+  "$NVCC" $NVFLAGS -c "$G/backend/cuda/kernels_math.cu" -o "$SCRATCH/kernels_math.o" &
+  "$NVCC" $NVFLAGS -c "$G/backend/cuda/kernels_utils.cu" -o "$SCRATCH/kernels_utils.o" &
+  wait
+  if [ -f "$SCRATCH/kernels_math.o" ] && [ -f "$SCRATCH/kernels_utils.o" ] && [ -n "$OPENBLAS" ]; then
+    g++ $CXXFLAGS "$HERE/ref_harness.cpp" "$SCRATCH/kernels_math.o" "$SCRATCH/kernels_utils.o" -o "$OUT/ref_harness_cuda" \
+        "$OPENBLAS" -Wl,--disable-new-dtags -Wl,-rpath,"$BLASDIR" -Wl,--allow-shlib-undefined \
+        -L/usr/local/cuda/lib64 -lcudart -lcublas -lcurand -Wl,-rpath,/usr/local/cuda/lib64 -fopenmp
+    echo "build_ref: wrote $OUT/ref_harness_cuda"
+  else
+    echo "build_ref: the reference's .cu files did not compile here; no ref_harness_cuda"
+  fi
+fi

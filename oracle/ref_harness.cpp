@@ -21,6 +21,9 @@
 //        Writes <outprefix>_loss.txt, _grads<k>.ckpt and _weights<k>.ckpt for k in {1, steps}, _time.txt.
 //   ref_harness ops  in.ckpt out.ckpt
 //        Runs every op-level case whose inputs are present in in.ckpt (see run_ops()).
+//   ref_harness gptcuda <arch> V T C H L F B steps warmup tokens.i64        (only in the build that links the reference's .cu files)
+//        Times the reference's CUDA path the way train.cpp:136-161 drives it: model.to(gpu), softmax_crossentropy_fast,
+//        clip, AdamW fast branch; prints one line "tokens_per_s <v> ms_per_step <t> hwm_gb <g> loss <l>".
 #include "gradc/gradc.hpp"
 
 #include <chrono>
@@ -195,6 +198,49 @@ static int run_gpt(Model& model, int64_t V, int64_t T, int64_t B, int64_t steps,
     return 0;
 }
 
+// The reference's own CUDA path on one micro-batch per step (train.cpp:136-161 with grad_accum_steps = 1).
+template <class Model>
+static int run_gpt_cuda(Model& model, int64_t V, int64_t T, int64_t B, int64_t steps, int64_t warm, const std::string& tpath) {
+    Device cpu(DeviceType::CPU), gpu(DeviceType::CUDA, 0);
+    std::ifstream tin(tpath, std::ios::binary);
+    if (!tin) throw std::runtime_error("cannot open tokens " + tpath);
+    Tensor<int64_t> Xh({B, T}, cpu, uninitialized), Yh({B, T}, cpu, uninitialized);
+    tin.read(reinterpret_cast<char*>(Xh._get_storage()->data()), sizeof(int64_t) * B * T);
+    tin.read(reinterpret_cast<char*>(Yh._get_storage()->data()), sizeof(int64_t) * B * T);
+    if (!tin) throw std::runtime_error("token file too short");
+    // N(0, 0.02)-like weights without the reference's RNG: a fixed low-discrepancy fill, so that probabilities and gradients are not degenerate
+    for (auto& [name, p] : model.named_parameters()) {
+        float* w = p->tensor()._get_storage()->data();
+        const int64_t n = p->tensor().volume();
+        if (p->tensor().shape().size() < 2) continue;  // biases 0, gamma 1, beta 0 stay
+        uint64_t h = std::hash<std::string>{}(name) | 1u;
+        for (int64_t i = 0; i < n; ++i) { h = h * 6364136223846793005ull + 1442695040888963407ull; w[i] = 0.02f * 1.7320508f * (static_cast<float>((h >> 40) & 0xffffff) / 8388608.0f - 1.0f); }
+    }
+    model.to(gpu);
+    AdamW<float> opt(model.named_parameters(), 3e-4f, 0.9f, 0.95f, 0.1f, 1e-5f);
+    GlobalNormClipper<float> clipper(1.0f);
+    Tensor<int64_t> X = Xh.to(gpu), Y = Yh.to(gpu);
+    X.realize(); Y.realize();
+    float last = 0.0f;
+    std::chrono::high_resolution_clock::time_point t0;
+    for (int64_t step = 0; step < warm + steps; ++step) {
+        if (step == warm) { cudaDeviceSynchronize(); t0 = std::chrono::high_resolution_clock::now(); }
+        model.zero_grad();
+        Tensor<float> logits = model.forward(X);
+        Tensor<float> loss = softmax_crossentropy_fast<float>(logits, Y, 1e-5f);
+        loss.realize();
+        loss.backward();
+        clipper.normalize(model.parameters());
+        opt.step();
+        if (step == warm + steps - 1) last = loss.item();
+    }
+    cudaDeviceSynchronize();
+    const double ms = std::chrono::duration<double, std::milli>(std::chrono::high_resolution_clock::now() - t0).count() / static_cast<double>(steps);
+    std::cout.precision(9);
+    std::cout << "tokens_per_s " << (B * T) / (ms / 1e3) << " ms_per_step " << ms << " hwm_gb " << CUDAMemPool::get().get_hwm_gb() << " loss " << last << std::endl;
+    return 0;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Op-level cases. Each reads "<case>.<input>" tensors and writes "<case>.<output>" tensors.
 // ------------------------------------------------------------------------------------------------
@@ -366,6 +412,20 @@ int main(int argc, char** argv) {
             }
             std::cerr << "unknown arch " << arch << "\n";
             return 2;
+        }
+        if (mode == "gptcuda") {
+            if (argc != 13) { std::cerr << "usage: ref_harness gptcuda arch V T C H L F B steps warmup tokens\n"; return 2; }
+            std::string arch = argv[2];
+            int64_t V = std::stoll(argv[3]), T = std::stoll(argv[4]), C = std::stoll(argv[5]), H = std::stoll(argv[6]);
+            int64_t L = std::stoll(argv[7]), F = std::stoll(argv[8]), B = std::stoll(argv[9]);
+            int64_t steps = std::stoll(argv[10]), warm = std::stoll(argv[11]);
+            if (arch == "lngelu") {
+                LNGPT model(V, T, C, H, L, F, 1e-5f);
+                return run_gpt_cuda(model, V, T, B, steps, warm, argv[12]);
+            }
+            ZerosInit<float> z;
+            GPT<float> model(V, T, C, H, L, z, z, 1e-5f);
+            return run_gpt_cuda(model, V, T, B, steps, warm, argv[12]);
         }
         std::cerr << "unknown mode\n";
         return 2;
