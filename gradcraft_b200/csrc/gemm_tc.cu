@@ -123,6 +123,54 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {  // A from tensor memory
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]),
+                 "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+
+// One row of a landed A tile -> this thread's TMEM lane: 16 columns of t (x truncated to TF32), 8 of bf16(x) pairs, 8 of
+// bf16(x - t) pairs (lower k in the lower half).  `row` is the tile row = TMEM lane; taddr addresses that lane's quarter.
+template <bool MN>
+__device__ __forceinline__ void split_a_to_tmem(const uint8_t* raw, uint32_t taddr, int row) {
+    float x[16];
+    if (!MN) {  // 64-byte rows, 16-byte chunk index XOR ((row >> 1) & 3)
+        const uint8_t* r = raw + row * 64;
+        const int sw = (row >> 1) & 3;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float4 v = *reinterpret_cast<const float4*>(r + ((c ^ sw) << 4));
+            x[4 * c] = v.x; x[4 * c + 1] = v.y; x[4 * c + 2] = v.z; x[4 * c + 3] = v.w;
+        }
+    } else {  // boxes of 16 k-rows x 32 floats, 32-byte unit index XOR (k & 3)
+        const uint8_t* box = raw + (row >> 5) * 2048;
+        const int j = row & 31;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) x[k] = *reinterpret_cast<const float*>(box + k * 128 + ((((j >> 3) ^ (k & 3)) << 5) | ((j & 7) << 2)));
+    }
+    uint32_t t[16], bg[8], sm[8];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) t[k] = __float_as_uint(x[k]) & 0xffffe000u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        bg[i] = pack_bf16(x[2 * i], x[2 * i + 1]);
+        sm[i] = pack_bf16(x[2 * i] - __uint_as_float(t[2 * i]), x[2 * i + 1] - __uint_as_float(t[2 * i + 1]));
+    }
+    tmem_st16(taddr, t);
+    tmem_st8(taddr + 16, bg);
+    tmem_st8(taddr + 24, sm);
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Split mode 2 ("TF32 + 2 x BF16"): x = t + s with t = x truncated to TF32 (what the tensor core reads from the raw tile) and
 // s = x - t (exact).  a b ~ t_a t_b (one TF32 product) + bf16(s_a) bf16(b) + bf16(a) bf16(s_b) (two BF16 products at twice
 // the TF32 rate): two thirds of the tensor time of three TF32 products, error ~ 2^-19 of a product instead of 2^-22,
@@ -195,12 +243,20 @@ struct RoleTrace {
 #define TR_END()
 #endif
 
-template <int BN>
+// A_TM: the A operand reaches the tensor core through tensor memory instead of shared memory (split mode 2 only).  The
+// splitter warps read each landed A tile once and store t, bf16(x) and bf16(s) into 32 TMEM columns per stage (16 + 8 + 8);
+// the tensor core then fetches only B from shared memory and nothing of A is written back to it, which takes 40 % off the
+// shared-memory traffic of a narrow tile — the resource these kernels run out of first.
+template <int BN, bool A_TM = false>
 struct TcSmem {
-    static constexpr int STAGES = BN == 64 ? 3 : 4;  // narrow tiles: two CTAs per SM (two issuer / producer threads) beat one deeper ring (measured)
+    static constexpr int STAGES = A_TM ? (BN == 64 ? 4 : 8) : (BN == 64 ? 3 : 4);  // narrow tiles: two CTAs per SM (two issuer / producer threads) beat one deeper ring (measured)
     static constexpr int A_BYTES = TC_BM * TC_BK * 4;  // 8 KB
     static constexpr int B_BYTES = BN * TC_BK * 4;
-    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;  // big + small of each operand
+    static constexpr int B_OFF = A_TM ? A_BYTES : 2 * A_BYTES;     // raw A [+ its twin], then raw B + its twin
+    static constexpr int STAGE_BYTES = B_OFF + 2 * B_BYTES;
+    static constexpr int TMEM_COLS = A_TM ? (BN == 64 ? 256 : 512) : 2 * BN;  // two accumulators [+ STAGES x 32 columns of A]
+    static constexpr int A_TMEM_COL0 = 2 * BN;
+    static_assert(!A_TM || (BN <= 128 && A_TMEM_COL0 + STAGES * 32 <= TMEM_COLS), "A stages do not fit beside the accumulators");
     static constexpr int EPI_PITCH = 36;                           // floats per staged row: 32 + 4 keeps float4 alignment and spreads banks
     static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;       // one 32 x 32 transposition buffer per epilogue warp
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
@@ -265,9 +321,9 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int64_t w, in
 // Persistent: CTA c processes work items c, c + gridDim.x, ... in panels of TC_GROUP_M row tiles.  The accumulator is double-buffered in TMEM (2 x BN columns): the
 // epilogue warps drain tile i while the issuer already accumulates tile i + 1.
 // A_MN: A is stored K x M (contiguous along M); B_MN: B is stored K x N (contiguous along N).
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool A_TM>
 __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
-    using S = TcSmem<BN>;
+    using S = TcSmem<BN, A_TM>;
     constexpr int TC_STAGES = S::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -289,7 +345,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {  // TMEM allocation is warp-wide
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)S::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -311,7 +367,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                     const uint32_t ph = (it / TC_STAGES) & 1u;
                     ok = TR_WAIT(mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1));
                     if (!ok) break;
-                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
+                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + S::B_OFF;
                     mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES);
                     const int k0 = (tc.kb0 + i) * TC_BK;
                     if (A_MN) {
@@ -354,7 +410,17 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                     if (ok && p.split_mode) ok = TR_WAIT(mbar_wait(conv_bar(s), ph, p.status, 2));
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
+                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + S::B_OFF;
+                    if constexpr (A_TM) {  // A from tensor memory (K-major there whatever its storage order), B and its BF16 twin from shared memory
+                        const uint32_t a0 = tmem_base + S::A_TMEM_COL0 + s * 32, tb = sb + S::B_BYTES;
+#pragma unroll
+                        for (int j = 0; j < TC_BK / 8; ++j) {
+                            const uint32_t b_off = B_MN ? j * 1024 : j * 32;
+                            umma_tf32_ts(d_tmem, a0 + 8 * j, B_MN ? make_desc(sb + b_off, 2048, 512, 1) : make_desc(sb + b_off, 16, 512, 4), idesc & ~(1u << 15), (i | j) ? 1u : 0u);
+                        }
+                        umma_bf16_ts(d_tmem, a0 + 24, make_desc(tb, 128, 256, 0), idesc_bf, 1u);
+                        umma_bf16_ts(d_tmem, a0 + 16, make_desc(tb + S::B_BYTES / 2, 128, 256, 0), idesc_bf, 1u);
+                    } else {
 #pragma unroll
                     for (int j = 0; j < TC_BK / 8; ++j) {
                         const uint32_t a_off = A_MN ? j * 1024 : j * 32, b_off = B_MN ? j * 1024 : j * 32;
@@ -374,6 +440,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                         const uint32_t ta = sa + S::A_BYTES, tb = sb + S::B_BYTES;  // twin tiles: bf16(x) then bf16(x - trunc(x))
                         umma_bf16(d_tmem, make_desc(ta + S::A_BYTES / 2, 128, 256, 0), make_desc(tb, 128, 256, 0), idesc_bf, 1u);
                         umma_bf16(d_tmem, make_desc(ta, 128, 256, 0), make_desc(tb + S::B_BYTES / 2, 128, 256, 0), idesc_bf, 1u);
+                    }
                     }
                     umma_commit(empty_bar(s));  // the stage may be refilled once these MMAs have read it
                 }
@@ -415,10 +482,17 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                         }
                     }
                 };
-                if (p.split_mode == 2) {
+                if constexpr (A_TM) {
+                    uint8_t* st = gen_base + s * S::STAGE_BYTES;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");  // the MMAs that read this TMEM stage last round have completed (empty -> TMA -> full)
+                    const int row = 32 * (warp & 3) + lane;                          // a warp reaches the TMEM lanes of its quarter only
+                    split_a_to_tmem<A_MN>(st, tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + S::A_TMEM_COL0 + s * 32, row);
+                    split_hybrid<B_MN, BN>(st + S::B_OFF, st + S::B_OFF + S::B_BYTES, t);
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                } else if (p.split_mode == 2) {
                     uint8_t* st = gen_base + s * S::STAGE_BYTES;
                     split_hybrid<A_MN, TC_BM>(st, st + S::A_BYTES, t);
-                    split_hybrid<B_MN, BN>(st + 2 * S::A_BYTES, st + 2 * S::A_BYTES + S::B_BYTES, t);
+                    split_hybrid<B_MN, BN>(st + S::B_OFF, st + S::B_OFF + S::B_BYTES, t);
                 } else {
                     split_tile(stage, S::A_BYTES / 16, S::A_BYTES / 16);
                     split_tile(stage + 2 * (S::A_BYTES / 16), S::B_BYTES / 16, S::B_BYTES / 16);
@@ -538,7 +612,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
     }
 }
 
@@ -898,12 +972,12 @@ bool gemm_tc_eligible(bool ta, bool tb, const GemmArgs& g) {
     return true;
 }
 
-template <int BN>
+template <int BN, bool A_TM>
 static int launch_bn(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid) {
-    const size_t smem = TcSmem<BN>::TOTAL;
+    const size_t smem = TcSmem<BN, A_TM>::TOTAL;
 #define GCB_TC(AM, BMN)                                                                                                   \
     do {                                                                                                                  \
-        auto kfn = gemm_tc_kernel<BN, AM, BMN>;                                                                           \
+        auto kfn = gemm_tc_kernel<BN, AM, BMN, A_TM>;                                                                     \
         static bool attr_done = false;                                                                                    \
         if (!attr_done) { GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_done = true; } \
         kfn<<<grid, TC_THREADS, smem, ctx->stream>>>(ma, mb, p);                                                          \
@@ -1010,13 +1084,15 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
         p.work_items = (int64_t)p.kept_per_batch * batches;
     }
     p.split_mode = ctx->gemm_split_mode;
+    static const int a_tmem_env = [] { const char* e = getenv("GRADC_TC_ATMEM"); return e ? atoi(e) : 1; }();
+    const bool a_tmem = a_tmem_env != 0 && p.split_mode == 2 && BN <= 128;  // narrow tiles: A through tensor memory
     dim3 grid((unsigned)std::min<int64_t>(p.work_items, (int64_t)kSMs * (BN == 64 ? 2 : 1)), 1, 1);
     p.loop_end = g.causal >= 2 ? (p.work_items + grid.x - 1) / grid.x * grid.x : p.work_items;  // snake order: whole rounds
     int rc;
     if (use_pair) rc = launch_pair(ctx, ta, tb, ma, mb, p);
-    else if (BN == 256) rc = launch_bn<256>(ctx, ta, tb, ma, mb, p, grid);
-    else if (BN == 128) rc = launch_bn<128>(ctx, ta, tb, ma, mb, p, grid);
-    else rc = launch_bn<64>(ctx, ta, tb, ma, mb, p, grid);
+    else if (BN == 256) rc = launch_bn<256, false>(ctx, ta, tb, ma, mb, p, grid);
+    else if (BN == 128) rc = a_tmem ? launch_bn<128, true>(ctx, ta, tb, ma, mb, p, grid) : launch_bn<128, false>(ctx, ta, tb, ma, mb, p, grid);
+    else rc = a_tmem ? launch_bn<64, true>(ctx, ta, tb, ma, mb, p, grid) : launch_bn<64, false>(ctx, ta, tb, ma, mb, p, grid);
     if (rc) return rc;
     rc = after_launch(ctx, "gemm_tc");
     if (rc) return rc;
