@@ -46,6 +46,7 @@ struct TcParams {
     int64_t work_items;  // tiles to compute (x splits)
     int64_t loop_end;    // bound of the persistent loop: work_items, rounded up to whole rounds where the snake order needs it
     int kept_per_batch;  // causal mode 1: tiles per batch at or below the diagonal
+    int a_chunked, b_chunked;  // MN-major operand described to TMA as (32 floats, k, chunk of 32, batches): one copy fills all 32-float chunks of a tile
     int causal;          // see GemmArgs::causal
     int split_mode;      // 2 (default): one TF32 product of the truncated parts + two BF16 cross products (split_hybrid below);
                          // 1: three TF32 products; big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
@@ -79,6 +80,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+                 "r"(c4)
                  : "memory");
 }
 __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
@@ -371,12 +377,16 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
                     mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES);
                     const int k0 = (tc.kb0 + i) * TC_BK;
                     if (A_MN) {
+                        if (p.a_chunked) tma_load_5d(sa, &map_a, full_bar(s), 0, k0, tc.m0 / 32, tc.b_in, tc.b_out);
+                        else
 #pragma unroll
                         for (int c = 0; c < TC_BM / 32; ++c) tma_load_4d(sa + c * 2048, &map_a, full_bar(s), tc.m0 + 32 * c, k0, tc.b_in, tc.b_out);
                     } else {
                         tma_load_4d(sa, &map_a, full_bar(s), k0, tc.m0, tc.b_in, tc.b_out);
                     }
                     if (B_MN) {
+                        if (p.b_chunked) tma_load_5d(sb, &map_b, full_bar(s), 0, k0, tc.n0 / 32, tc.b_in, tc.b_out);
+                        else
 #pragma unroll
                         for (int c = 0; c < BN / 32; ++c) tma_load_4d(sb + c * 2048, &map_b, full_bar(s), tc.n0 + 32 * c, k0, tc.b_in, tc.b_out);
                     } else {
@@ -638,15 +648,31 @@ __device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc,
 __device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void umma_tf32_pair_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {  // A: each CTA's 128 rows from its own tensor memory
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {  // arrives on the barrier at this offset in both CTAs of the pair
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
 
-struct PairSmem {
-    static constexpr int BN = 256, STAGES = 6;
+// A_TM (split mode 2): A goes through tensor memory as in the single-CTA kernel.  The 512 TMEM columns then hold ONE
+// 256-column accumulator and eight 32-column A stages, so the epilogue of a tile no longer overlaps the next tile's MMAs;
+// what is gained is 30 % less shared-memory traffic per K block, the resource the pair kernel runs out of first.
+template <bool A_TM>
+struct PairSmemT {
+    static constexpr int BN = 256, STAGES = A_TM ? 8 : 6;
+    // A_TM: warps 2..5 move A into tensor memory while warps 6..9 split B; the epilogue warps follow (10..13)
+    static constexpr int SPLIT_WARPS = A_TM ? 8 : 4;
+    static constexpr int THREADS = 32 * (2 + SPLIT_WARPS + 4);
+    static constexpr int NACC = A_TM ? 1 : 2;                // accumulators in TMEM
+    static constexpr int A_TMEM_COL0 = 256;
     static constexpr int A_BYTES = TC_BM * TC_BK * 4;        // this CTA's 128 rows
     static constexpr int B_BYTES = (BN / 2) * TC_BK * 4;     // this CTA's half of the B tile
-    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    static constexpr int B_OFF = A_TM ? A_BYTES : 2 * A_BYTES;
+    static constexpr int STAGE_BYTES = B_OFF + 2 * B_BYTES;
     static constexpr int EPI_PITCH = 36;
     static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
@@ -676,10 +702,10 @@ __device__ __forceinline__ TileCoord pair_tile_coord(const TcParams& p, int64_t 
     return t;
 }
 
-template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
-    using S = PairSmem;
-    constexpr int BN = S::BN, NST = S::STAGES;
+template <bool A_MN, bool B_MN, bool A_TM>
+__global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+    using S = PairSmemT<A_TM>;
+    constexpr int BN = S::BN, NST = S::STAGES, NACC = S::NACC;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -697,7 +723,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
     const int64_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(conv_bar(s), 8); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(conv_bar(s), 2 * S::SPLIT_WARPS); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -726,16 +752,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
                     const uint32_t ph = (it / NST) & 1u;
                     ok = TR_WAIT(mbar_wait(empty_bar(s), ph ^ 1u, p.status, 11));
                     if (!ok) break;
-                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
+                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + S::B_OFF;
                     mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES);
                     const int k0 = (tc.kb0 + i) * TC_BK;
                     if (A_MN) {
+                        if (p.a_chunked) tma_load_5d(sa, &map_a, full_bar(s), 0, k0, m0 / 32, tc.b_in, tc.b_out);
+                        else
 #pragma unroll
                         for (int c = 0; c < 4; ++c) tma_load_4d(sa + c * 2048, &map_a, full_bar(s), m0 + 32 * c, k0, tc.b_in, tc.b_out);
                     } else {
                         tma_load_4d(sa, &map_a, full_bar(s), k0, m0, tc.b_in, tc.b_out);
                     }
                     if (B_MN) {
+                        if (p.b_chunked) tma_load_5d(sb, &map_b, full_bar(s), 0, k0, n0 / 32, tc.b_in, tc.b_out);
+                        else
 #pragma unroll
                         for (int c = 0; c < 4; ++c) tma_load_4d(sb + c * 2048, &map_b, full_bar(s), n0 + 32 * c, k0, tc.b_in, tc.b_out);
                     } else {
@@ -756,8 +786,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
             for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
                 const TileCoord tc = pair_tile_coord(p, w);
                 if (tc.skip) continue;
-                const uint32_t buf = lt & 1u;
-                ok = mbar_wait(acc_empty_bar(buf), ((lt >> 1) & 1u) ^ 1u, p.status, 15);
+                const uint32_t buf = lt % NACC;
+                ok = mbar_wait(acc_empty_bar(buf), ((lt / NACC) & 1u) ^ 1u, p.status, 15);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + buf * BN;
@@ -767,7 +797,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
                     ok = TR_WAIT(mbar_wait(conv_bar(s), ph, p.status, 12));  // both CTAs' tiles landed and were split
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + 2 * S::A_BYTES;
+                    const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + S::B_OFF;
+                    if constexpr (A_TM) {
+                        const uint32_t a0 = tmem_base + S::A_TMEM_COL0 + s * 32, tb = sb + S::B_BYTES;
+#pragma unroll
+                        for (int j = 0; j < TC_BK / 8; ++j) {
+                            const uint32_t b_off = B_MN ? j * 1024 : j * 32;
+                            umma_tf32_pair_ts(d_tmem, a0 + 8 * j, B_MN ? make_desc(sb + b_off, 2048, 512, 1) : make_desc(sb + b_off, 16, 512, 4), idesc & ~(1u << 15), (i | j) ? 1u : 0u);
+                        }
+                        umma_bf16_pair_ts(d_tmem, a0 + 24, make_desc(tb, 128, 256, 0), idesc_bf, 1u);
+                        umma_bf16_pair_ts(d_tmem, a0 + 16, make_desc(tb + S::B_BYTES / 2, 128, 256, 0), idesc_bf, 1u);
+                    } else {
 #pragma unroll
                     for (int j = 0; j < TC_BK / 8; ++j) {
                         const uint32_t a_off = A_MN ? j * 1024 : j * 32, b_off = B_MN ? j * 1024 : j * 32;
@@ -788,6 +828,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
                         umma_bf16_pair(d_tmem, make_desc(ta + S::A_BYTES / 2, 128, 256, 0), make_desc(tb, 128, 256, 0), idesc_bf, 1u);
                         umma_bf16_pair(d_tmem, make_desc(ta, 128, 256, 0), make_desc(tb + S::B_BYTES / 2, 128, 256, 0), idesc_bf, 1u);
                     }
+                    }
                     umma_commit_pair(empty_bar(s));
                 }
                 if (ok) umma_commit_pair(acc_full_bar(buf));
@@ -795,9 +836,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
             }
             TR_END();
         }
-    } else if (warp < 6) {
+    } else if (warp < 2 + S::SPLIT_WARPS) {
         // ---------------- splitter (own A rows, own half of B) ----------------
-        const int t = threadIdx.x - 64;
+        const int t = (threadIdx.x - 64) & 127;
         uint32_t it = 0;
         bool ok = true;
         TR_BEGIN(2);
@@ -817,10 +858,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
                         big[t + 128 * q + n_vec] = make_float4(round_tf32(x.x - trunc_tf32(x.x)), round_tf32(x.y - trunc_tf32(x.y)), round_tf32(x.z - trunc_tf32(x.z)), round_tf32(x.w - trunc_tf32(x.w)));
                     }
                 };
-                if (p.split_mode == 2) {
+                if constexpr (A_TM) {
+                    uint8_t* st = gen_base + s * S::STAGE_BYTES;
+                    if (warp < 6) {  // A rows of this warp's TMEM lane quarter
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        split_a_to_tmem<A_MN>(st, tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + S::A_TMEM_COL0 + s * 32, 32 * (warp & 3) + lane);
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    } else {
+                        split_hybrid<B_MN, BN / 2>(st + S::B_OFF, st + S::B_OFF + S::B_BYTES, t);
+                    }
+                } else if (p.split_mode == 2) {
                     uint8_t* st = gen_base + s * S::STAGE_BYTES;
                     split_hybrid<A_MN, TC_BM>(st, st + S::A_BYTES, t);
-                    split_hybrid<B_MN, BN / 2>(st + 2 * S::A_BYTES, st + 2 * S::A_BYTES + S::B_BYTES, t);
+                    split_hybrid<B_MN, BN / 2>(st + S::B_OFF, st + S::B_OFF + S::B_BYTES, t);
                 } else {
                     split_tile(stage, S::A_BYTES / 16);
                     split_tile(stage + 2 * (S::A_BYTES / 16), S::B_BYTES / 16);
@@ -844,8 +894,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
         for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
             const TileCoord tc = pair_tile_coord(p, w);
             if (tc.skip) continue;
-            const uint32_t buf = lt & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 14)) != 0;
+            const uint32_t buf = lt % NACC;
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt / NACC) & 1u, p.status, 14)) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float* cbase = to_partial ? p.partial + (int64_t)tc.split * p.M * p.N : p.C + (int64_t)tc.b_out * p.c_so + (int64_t)tc.b_in * p.c_si;
@@ -942,16 +992,32 @@ static EncodeTiledFn get_encode(gcb_ctx* ctx) {
     return (EncodeTiledFn)fn;
 }
 
-// 4-D map over one GEMM operand: (contiguous axis, other matrix axis, batch inner, batch outer)
-static bool encode_operand(EncodeTiledFn enc, CUtensorMap* map, const float* ptr, bool mn_major, int64_t rows_mn, int64_t K, int64_t ld, int64_t s_in, int64_t s_out, int64_t n_in, int64_t n_out, int tile_rows) {
+// Tensor map over one GEMM operand.  K-major: (k, row, batch inner, batch outer), box 16 x tile_rows.  MN-major: when the
+// row count is a multiple of 32, a 5-D view (32 floats, k, chunk of 32, batches) whose box 32 x 16 x tile_rows/32 fills every
+// 32-float chunk of the tile with one copy (*chunked = 1); otherwise the 4-D (row, k, batches) view, one copy per chunk.
+static bool encode_operand(EncodeTiledFn enc, CUtensorMap* map, const float* ptr, bool mn_major, int64_t rows_mn, int64_t K, int64_t ld, int64_t s_in, int64_t s_out, int64_t n_in, int64_t n_out, int tile_rows,
+                           int* chunked) {
+    const cuuint64_t row_bytes = (cuuint64_t)ld * 4;
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    *chunked = 0;
+    if (mn_major && rows_mn % 32 == 0) {
+        cuuint64_t dims[5] = {32, (cuuint64_t)K, (cuuint64_t)(rows_mn / 32), (cuuint64_t)n_in, (cuuint64_t)n_out};
+        cuuint64_t strides[4] = {row_bytes, 128, n_in > 1 ? (cuuint64_t)s_in * 4 : row_bytes * (cuuint64_t)K, n_out > 1 ? (cuuint64_t)s_out * 4 : row_bytes * (cuuint64_t)K};
+        if (strides[2] == 0) strides[2] = 16;
+        if (strides[3] == 0) strides[3] = 16;
+        cuuint32_t box[5] = {32u, (cuuint32_t)TC_BK, (cuuint32_t)(tile_rows / 32), 1u, 1u};
+        if (enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+            *chunked = 1;
+            return true;
+        }
+    }
     const cuuint64_t inner = mn_major ? (cuuint64_t)rows_mn : (cuuint64_t)K, outer = mn_major ? (cuuint64_t)K : (cuuint64_t)rows_mn;
     cuuint64_t dims[4] = {inner, outer, (cuuint64_t)n_in, (cuuint64_t)n_out};
-    const cuuint64_t row_bytes = (cuuint64_t)ld * 4;
     cuuint64_t strides[3] = {row_bytes, n_in > 1 ? (cuuint64_t)s_in * 4 : row_bytes * outer, n_out > 1 ? (cuuint64_t)s_out * 4 : row_bytes * outer};
     if (strides[1] == 0) strides[1] = 16;
     if (strides[2] == 0) strides[2] = 16;
     cuuint32_t box[4] = {mn_major ? 32u : (cuuint32_t)TC_BK, mn_major ? (cuuint32_t)TC_BK : (cuuint32_t)tile_rows, 1u, 1u};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -991,12 +1057,13 @@ static int launch_bn(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, cons
     return GCB_OK;
 }
 
+template <bool A_TM>
 static int launch_pair(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
-    const size_t smem = PairSmem::TOTAL;
+    const size_t smem = PairSmemT<A_TM>::TOTAL;
     cudaLaunchConfig_t cfg = {};
     const int64_t pairs = std::min<int64_t>(p.work_items, kSMs / 2);
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    cfg.blockDim = dim3(TC_THREADS, 1, 1);
+    cfg.blockDim = dim3(PairSmemT<A_TM>::THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -1008,7 +1075,7 @@ static int launch_pair(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, co
     cfg.numAttrs = 1;
 #define GCB_PAIR(AM, BMN)                                                                                                   \
     do {                                                                                                                    \
-        auto kfn = gemm_tc_pair_kernel<AM, BMN>;                                                                            \
+        auto kfn = gemm_tc_pair_kernel<AM, BMN, A_TM>;                                                                            \
         static bool attr_done = false;                                                                                      \
         static int max_clusters = 0;                                                                                        \
         if (!attr_done) {                                                                                                   \
@@ -1038,9 +1105,9 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     static const int pair_env = [] { const char* e = getenv("GRADC_TC_PAIR"); return e ? atoi(e) : 1; }();
     const bool use_pair = pair_env != 0 && BN == 256 && g.M > 128 && g.K >= 256 && !g.sm_probs;  // short K loops are epilogue-bound: nothing to gain from sharing B
     CUtensorMap ma, mb;
-    if (!encode_operand(enc, &ma, g.A, ta, g.M, g.K, g.lda, g.a_si, g.a_so, g.batch_inner, g.batch_outer, TC_BM)) return GCB_UNSUPPORTED;
-    if (!encode_operand(enc, &mb, g.B, !tb, g.N, g.K, g.ldb, g.b_si, g.b_so, g.batch_inner, g.batch_outer, use_pair ? 128 : BN)) return GCB_UNSUPPORTED;
     TcParams p;
+    if (!encode_operand(enc, &ma, g.A, ta, g.M, g.K, g.lda, g.a_si, g.a_so, g.batch_inner, g.batch_outer, TC_BM, &p.a_chunked)) return GCB_UNSUPPORTED;
+    if (!encode_operand(enc, &mb, g.B, !tb, g.N, g.K, g.ldb, g.b_si, g.b_so, g.batch_inner, g.batch_outer, use_pair ? 128 : BN, &p.b_chunked)) return GCB_UNSUPPORTED;
     p.M = g.M; p.N = g.N; p.K = g.K;
     p.alpha = g.alpha; p.beta = g.beta; p.bias = g.bias; p.C = g.C;
     p.ldc = g.ldc; p.c_so = g.c_so; p.c_si = g.c_si;
@@ -1086,10 +1153,11 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     p.split_mode = ctx->gemm_split_mode;
     static const int a_tmem_env = [] { const char* e = getenv("GRADC_TC_ATMEM"); return e ? atoi(e) : 1; }();
     const bool a_tmem = a_tmem_env != 0 && p.split_mode == 2 && BN <= 128;  // narrow tiles: A through tensor memory
+    static const int pair_tmem_env = [] { const char* e = getenv("GRADC_TC_PAIR_ATMEM"); return e ? atoi(e) : 1; }();
     dim3 grid((unsigned)std::min<int64_t>(p.work_items, (int64_t)kSMs * (BN == 64 ? 2 : 1)), 1, 1);
     p.loop_end = g.causal >= 2 ? (p.work_items + grid.x - 1) / grid.x * grid.x : p.work_items;  // snake order: whole rounds
     int rc;
-    if (use_pair) rc = launch_pair(ctx, ta, tb, ma, mb, p);
+    if (use_pair) rc = (pair_tmem_env != 0 && p.split_mode == 2) ? launch_pair<true>(ctx, ta, tb, ma, mb, p) : launch_pair<false>(ctx, ta, tb, ma, mb, p);
     else if (BN == 256) rc = launch_bn<256, false>(ctx, ta, tb, ma, mb, p, grid);
     else if (BN == 128) rc = a_tmem ? launch_bn<128, true>(ctx, ta, tb, ma, mb, p, grid) : launch_bn<128, false>(ctx, ta, tb, ma, mb, p, grid);
     else rc = a_tmem ? launch_bn<64, true>(ctx, ta, tb, ma, mb, p, grid) : launch_bn<64, false>(ctx, ta, tb, ma, mb, p, grid);
