@@ -255,7 +255,11 @@ struct RoleTrace {
 // shared-memory traffic of a narrow tile — the resource these kernels run out of first.
 template <int BN, bool A_TM = false>
 struct TcSmem {
-    static constexpr int STAGES = A_TM ? (BN == 64 ? 4 : 8) : (BN == 64 ? 3 : 4);  // narrow tiles: two CTAs per SM (two issuer / producer threads) beat one deeper ring (measured)
+    static constexpr int STAGES = A_TM ? (BN == 64 ? 4 : 8) : (BN == 128 ? 4 : 3);  // narrow tiles: two CTAs per SM (two issuer / producer threads) beat one deeper ring (measured)
+    // 256-wide tiles are used for short K loops (attention scores / dS): their epilogue is the bottleneck, so eight warps
+    // share it, two per TMEM lane quarter with half of the columns each
+    static constexpr int EPI_WARPS = BN == 256 ? 8 : 4;
+    static constexpr int THREADS = 32 * (6 + EPI_WARPS);
     static constexpr int A_BYTES = TC_BM * TC_BK * 4;  // 8 KB
     static constexpr int B_BYTES = BN * TC_BK * 4;
     static constexpr int B_OFF = A_TM ? A_BYTES : 2 * A_BYTES;     // raw A [+ its twin], then raw B + its twin
@@ -264,7 +268,7 @@ struct TcSmem {
     static constexpr int A_TMEM_COL0 = 2 * BN;
     static_assert(!A_TM || (BN <= 128 && A_TMEM_COL0 + STAGES * 32 <= TMEM_COLS), "A stages do not fit beside the accumulators");
     static constexpr int EPI_PITCH = 36;                           // floats per staged row: 32 + 4 keeps float4 alignment and spreads banks
-    static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;       // one 32 x 32 transposition buffer per epilogue warp
+    static constexpr int EPI_BYTES = EPI_WARPS * 32 * EPI_PITCH * 4;  // one 32 x 32 transposition buffer per epilogue warp
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
     static constexpr int TOTAL = BAR_OFFSET + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
@@ -328,7 +332,7 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int64_t w, in
 // epilogue warps drain tile i while the issuer already accumulates tile i + 1.
 // A_MN: A is stored K x M (contiguous along M); B_MN: B is stored K x N (contiguous along N).
 template <int BN, bool A_MN, bool B_MN, bool A_TM>
-__global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+__global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
     using S = TcSmem<BN, A_TM>;
     constexpr int TC_STAGES = S::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -347,7 +351,7 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(conv_bar(s), 4); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), S::EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {  // TMEM allocation is warp-wide
@@ -515,8 +519,10 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
         TR_END();
     } else {
         // ---------------- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. +31, i.e. 32 rows of the tile ----------------
-        const int q = warp & 3;
-        float* stg = reinterpret_cast<float*>(gen_base + TC_STAGES * S::STAGE_BYTES) + q * 32 * S::EPI_PITCH;
+        const int q = warp & 3, ew = warp - 6;
+        constexpr int COLS_PER_WARP = BN / 32 / (S::EPI_WARPS / 4);  // 32-column blocks each warp of a lane quarter drains
+        const int c_begin = (ew >> 2) * COLS_PER_WARP, c_end = c_begin + COLS_PER_WARP;
+        float* stg = reinterpret_cast<float*>(gen_base + TC_STAGES * S::STAGE_BYTES) + ew * 32 * S::EPI_PITCH;
         const bool to_partial = p.splits > 1;
         const bool vec_ok = to_partial ? (p.N % 4 == 0) : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
         const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
@@ -538,17 +544,18 @@ __global__ void __launch_bounds__(TC_THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel
             const int64_t n_end = p.causal == 1 ? min(p.N, (int64_t)tc.m0 + TC_BM) : p.N;
             if (sm_probs) {  // pull this warp's 32 rows of the probability tile into L2 while the MMAs of the tile are still running
                 const int64_t row0 = (int64_t)tc.m0 + 32 * q;
-                const int lines = (int)((min(n_end, (int64_t)tc.n0 + BN) - tc.n0 + 31) / 32);
+                const int64_t col0 = (int64_t)tc.n0 + 32 * c_begin;
+                const int lines = (int)max((int64_t)0, (min(n_end, (int64_t)tc.n0 + 32 * c_end) - col0 + 31) / 32);
                 for (int i = lane; i < 32 * lines; i += 32) {
                     const int64_t r = row0 + i / lines;
-                    if (r < p.M) asm volatile("prefetch.global.L2 [%0];" ::"l"(sm_probs + (cbase - p.C) + r * ld + tc.n0 + 32 * (i % lines)));
+                    if (r < p.M) asm volatile("prefetch.global.L2 [%0];" ::"l"(sm_probs + (cbase - p.C) + r * ld + col0 + 32 * (i % lines)));
                 }
             }
             ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = c_begin; c < c_end; ++c) {
                 const int64_t nb = (int64_t)tc.n0 + 32 * c;
                 if (nb >= n_end) break;  // warp-uniform
                 const int64_t m_first = ((int64_t)tc.m0 + 32 * q) + sub_r, n = nb + sub_c;
@@ -663,10 +670,12 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {  // arrives on 
 // what is gained is 30 % less shared-memory traffic per K block, the resource the pair kernel runs out of first.
 template <bool A_TM>
 struct PairSmemT {
-    static constexpr int BN = 256, STAGES = A_TM ? 8 : 6;
+    static constexpr int BN = 256, STAGES = A_TM ? 7 : 6;
     // A_TM: warps 2..5 move A into tensor memory while warps 6..9 split B; the epilogue warps follow (10..13)
     static constexpr int SPLIT_WARPS = A_TM ? 8 : 4;
-    static constexpr int THREADS = 32 * (2 + SPLIT_WARPS + 4);
+    // A_TM has a single accumulator, so the time the epilogue holds it is exposed: eight warps drain it, two per lane quarter
+    static constexpr int EPI_WARPS = A_TM ? 8 : 4;
+    static constexpr int THREADS = 32 * (2 + SPLIT_WARPS + EPI_WARPS);
     static constexpr int NACC = A_TM ? 1 : 2;                // accumulators in TMEM
     static constexpr int A_TMEM_COL0 = 256;
     static constexpr int A_BYTES = TC_BM * TC_BK * 4;        // this CTA's 128 rows
@@ -674,7 +683,7 @@ struct PairSmemT {
     static constexpr int B_OFF = A_TM ? A_BYTES : 2 * A_BYTES;
     static constexpr int STAGE_BYTES = B_OFF + 2 * B_BYTES;
     static constexpr int EPI_PITCH = 36;
-    static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH * 4;
+    static constexpr int EPI_BYTES = EPI_WARPS * 32 * EPI_PITCH * 4;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
     static constexpr int TOTAL = BAR_OFFSET + 1024 + 256;
 };
@@ -724,7 +733,7 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(conv_bar(s), 2 * S::SPLIT_WARPS); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 8); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 2 * S::EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -883,8 +892,10 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
         TR_END();
     } else {
         // ---------------- epilogue: this CTA's 128 rows of the pair tile ----------------
-        const int q = warp & 3;
-        float* stg = reinterpret_cast<float*>(gen_base + NST * S::STAGE_BYTES) + q * 32 * S::EPI_PITCH;
+        const int q = warp & 3, ew = warp - (2 + S::SPLIT_WARPS);
+        constexpr int COLS_PER_WARP = BN / 32 / (S::EPI_WARPS / 4);
+        const int c_begin = (ew >> 2) * COLS_PER_WARP, c_end = c_begin + COLS_PER_WARP;
+        float* stg = reinterpret_cast<float*>(gen_base + NST * S::STAGE_BYTES) + ew * 32 * S::EPI_PITCH;
         const bool to_partial = p.splits > 1;
         const bool vec_ok = to_partial ? (p.N % 4 == 0) : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
         const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
@@ -904,7 +915,7 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
             const float* bias = to_partial ? nullptr : p.bias;
             const int64_t mrow0 = (int64_t)tc.m0 + 128 * (int)rank + 32 * q;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = c_begin; c < c_end; ++c) {
                 const int64_t nb = (int64_t)tc.n0 + 32 * c;
                 if (nb >= p.N) break;
                 float v[32];
@@ -1046,7 +1057,7 @@ static int launch_bn(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, cons
         auto kfn = gemm_tc_kernel<BN, AM, BMN, A_TM>;                                                                     \
         static bool attr_done = false;                                                                                    \
         if (!attr_done) { GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_done = true; } \
-        kfn<<<grid, TC_THREADS, smem, ctx->stream>>>(ma, mb, p);                                                          \
+        kfn<<<grid, TcSmem<BN, A_TM>::THREADS, smem, ctx->stream>>>(ma, mb, p);                                                          \
     } while (0)
     // A "transposed" (stored K x M) is MN-major; B "normal" (stored K x N) is MN-major
     if (ta && !tb) GCB_TC(true, true);
