@@ -172,6 +172,23 @@ int gct_optimizer_step(gct_trainer* tr, float* norm_out) {
     });
 }
 
+// Checkpoint files in the reference's format (nn/utils/checkpoint.hpp:12-77), as train.cpp:174-179 writes and :100-118 reads them.
+int gct_save_checkpoint(gct_trainer* tr, const char* model_path, const char* optim_path) {
+    return guarded([&] {
+        if (!tr || !model_path || !optim_path) throw std::runtime_error("gct_save_checkpoint: NULL argument");
+        Device cpu(DeviceType::CPU);
+        save_tensor_checkpoint(tr->model->state_dict(cpu), model_path);
+        save_tensor_checkpoint(tr->opt->state_dict(cpu), optim_path);
+    });
+}
+int gct_load_checkpoint(gct_trainer* tr, const char* model_path, const char* optim_path) {
+    return guarded([&] {
+        if (!tr || !model_path || !optim_path) throw std::runtime_error("gct_load_checkpoint: NULL argument");
+        tr->model->load_state_dict(load_tensor_checkpoint<float>(model_path));
+        tr->opt->load_state_dict(load_tensor_checkpoint<float>(optim_path));
+    });
+}
+
 int gct_sync(gct_trainer* tr) {
     return guarded([&] { gcb_check(gcb_ctx_sync(Backend::get().ctx(tr->gpu)), "gct_sync"); });
 }

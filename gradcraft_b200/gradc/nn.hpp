@@ -9,6 +9,11 @@
 //   * GlobalNormClipper::normalize is one sum-of-squares over the gradient arena and one scalar read-back.
 #pragma once
 
+#include <exception>
+#include <mutex>
+#include <thread>
+#include <deque>
+#include <condition_variable>
 #include <cmath>
 #include <filesystem>
 #include <fstream>
@@ -78,6 +83,27 @@ public:
 };
 
 // ---- module ------------------------------------------------------------------------------------------------------------
+// ---- arena-wide state transfer (checkpoints) ---------------------------------------------------------------------------
+// The reference copies every tensor of a state_dict with its own blocking cudaMemcpy (nn/base/module.hpp:68-97,
+// nn/optim/adam.hpp:171-240).  Arena-resident state moves as ONE copy per array; the per-tensor host tensors of the dict
+// are views into that single host buffer, so the on-disk format (nn/utils/checkpoint.hpp:12-77) is unchanged.
+inline std::shared_ptr<Storage<float>> arena_array_to_host(const ParamArena& a, const float* dev_array) {
+    auto host = std::make_shared<Storage<float>>(a.total, 0.0f, Device(DeviceType::CPU), true, false);
+    gcb_check(gcb_copy_d2h(Backend::get().ctx(a.device), host->data(), dev_array, sizeof(float) * (size_t)a.total), "arena download");
+    return host;
+}
+inline Tensor<float> host_slot_view(const std::shared_ptr<Storage<float>>& host, const ParamArena::Slot& s, const std::vector<int64_t>& shape) {
+    return Tensor<float>(shape, dense_strides(shape), s.offset, host, false);
+}
+// Overwrites the slots named by `entries` (slot index -> contiguous host data) in a device array of the arena: the current
+// contents are fetched once, patched on the host, and written back once.
+inline void arena_array_patch_from_host(const ParamArena& a, float* dev_array, const std::vector<std::pair<int, const float*>>& entries) {
+    if (entries.empty()) return;
+    auto host = arena_array_to_host(a, dev_array);
+    for (const auto& [slot, src] : entries) std::memcpy(host->data() + a.slots[slot].offset, src, sizeof(float) * (size_t)a.slots[slot].size);
+    gcb_check(gcb_copy_h2d(Backend::get().ctx(a.device), dev_array, host->data(), sizeof(float) * (size_t)a.total), "arena upload");
+}
+
 template <typename T>
 class Module {
 protected:
@@ -118,6 +144,14 @@ public:
     }
     std::unordered_map<std::string, Tensor<T>> state_dict(Device device = Device(DeviceType::CPU)) const {
         std::unordered_map<std::string, Tensor<T>> d;
+        if constexpr (std::is_same_v<T, float>) {
+            std::shared_ptr<ParamArena> a = whole_arena();
+            if (a && device.is_cpu()) {  // one download of the weight array; the dict holds views into it
+                auto host = arena_array_to_host(*a, a->w);
+                for (const auto& [name, p] : named_parameters()) d[name] = host_slot_view(host, a->slots[p->tensor()._get_state()->m_slot.slot], p->tensor().shape());
+                return d;
+            }
+        }
         for (const auto& [name, p] : named_parameters()) {
             Tensor<T> moved = p->tensor().to(device);
             moved.realize();
@@ -126,6 +160,27 @@ public:
         return d;
     }
     void load_state_dict(const std::unordered_map<std::string, Tensor<T>>& sd) {
+        if constexpr (std::is_same_v<T, float>) {
+            std::shared_ptr<ParamArena> a = whole_arena();
+            bool all_host = a != nullptr;
+            if (a) for (const auto& [name, t] : sd) all_host = all_host && t._get_state() != nullptr && t.device().is_cpu() && t.is_contiguous();
+            if (all_host) {  // host dict -> arena: one download, patch, one upload
+                std::vector<std::pair<int, const float*>> entries;
+                for (const auto& [name, p] : named_parameters()) {
+                    auto it = sd.find(name);
+                    if (it == sd.end()) {
+                        std::cout << "Warning: '" + name + "' is in the model, but couldn't find its counterpart in state_dict during loading." << std::endl;
+                        continue;
+                    }
+                    if (it->second.volume() != p->tensor().volume()) throw std::runtime_error("load_state_dict: size mismatch for " + name);
+                    Tensor<T> src = it->second;
+                    src.realize();
+                    entries.emplace_back(p->tensor()._get_state()->m_slot.slot, src.data_ptr());
+                }
+                arena_array_patch_from_host(*a, a->w, entries);
+                return;
+            }
+        }
         for (const auto& [name, p] : named_parameters()) {
             auto it = sd.find(name);
             if (it == sd.end()) {
@@ -213,6 +268,15 @@ public:
         int64_t n = 0;
         for (Parameter<T>* p : parameters()) n += p->tensor()._get_storage()->size();
         return n;
+    }
+    // The arena, when every slot of it is a parameter of this module and every parameter lives in it (null otherwise).
+    std::shared_ptr<ParamArena> whole_arena() const {
+        auto named = named_parameters();
+        if (named.empty()) return nullptr;
+        std::shared_ptr<ParamArena> a = named.begin()->second->tensor()._get_state()->m_slot.arena;
+        if (!a || a->slots.size() != named.size()) return nullptr;
+        for (const auto& [n, p] : named) if (p->tensor()._get_state()->m_slot.arena != a) return nullptr;
+        return a;
     }
     // The arena the parameters live in after to(CUDA) (null before).
     std::shared_ptr<ParamArena> arena() {
@@ -565,8 +629,17 @@ public:
             moved.realize();
             r[key] = moved.detach();
         };
-        for (auto& [n, t] : m_first_moment) put(n + ".adamw_first", t);
-        for (auto& [n, t] : m_second_moment) put(n + ".adamw_second", t);
+        if (m_arena && device.is_cpu()) {  // two downloads (m, v) for the whole optimizer state
+            auto hm = arena_array_to_host(*m_arena, m_arena->m), hv = arena_array_to_host(*m_arena, m_arena->v);
+            for (auto& [n, p] : this->m_named_params) {
+                const ParamArena::Slot& sl = m_arena->slots[p->tensor()._get_state()->m_slot.slot];
+                r[n + ".adamw_first"] = host_slot_view(hm, sl, p->tensor().shape());
+                r[n + ".adamw_second"] = host_slot_view(hv, sl, p->tensor().shape());
+            }
+        } else {
+            for (auto& [n, t] : m_first_moment) put(n + ".adamw_first", t);
+            for (auto& [n, t] : m_second_moment) put(n + ".adamw_second", t);
+        }
         put("beta1_exp", Tensor<T>(m_beta1_exp, Device(DeviceType::CPU)));
         put("beta2_exp", Tensor<T>(m_beta2_exp, Device(DeviceType::CPU)));
         return r;
@@ -583,8 +656,25 @@ public:
                 else { Tensor<T> d2 = t; copy_or_add(d2, make_contiguous(src), false); }
             }
         };
-        load(m_first_moment, ".adamw_first");
-        load(m_second_moment, ".adamw_second");
+        bool all_host = m_arena != nullptr;
+        if (m_arena) for (const auto& [k, t] : sd) all_host = all_host && t._get_state() != nullptr && t.device().is_cpu() && t.is_contiguous();
+        if (all_host) {
+            auto patch = [&](float* dev_array, const char* suffix) {
+                std::vector<std::pair<int, const float*>> entries;
+                for (auto& [n, p] : this->m_named_params) {
+                    auto it = sd.find(n + suffix);
+                    if (it == sd.end()) { std::cout << "Warning: '" + n + "' has no '" + suffix + "' entry in the optimizer state_dict." << std::endl; continue; }
+                    if (it->second.volume() != p->tensor().volume()) throw std::runtime_error("AdamW::load_state_dict: size mismatch for " + n + suffix);
+                    entries.emplace_back(p->tensor()._get_state()->m_slot.slot, it->second.data_ptr());
+                }
+                arena_array_patch_from_host(*m_arena, dev_array, entries);
+            };
+            patch(m_arena->m, ".adamw_first");
+            patch(m_arena->v, ".adamw_second");
+        } else {
+            load(m_first_moment, ".adamw_first");
+            load(m_second_moment, ".adamw_second");
+        }
         auto b1 = sd.find("beta1_exp"), b2 = sd.find("beta2_exp");
         if (b1 == sd.end()) throw std::runtime_error("Tried loading AdamW optimizer with state_dict without key 'beta1_exp'");
         if (b2 == sd.end()) throw std::runtime_error("Tried loading AdamW optimizer with state_dict without key 'beta2_exp'");
@@ -697,8 +787,48 @@ public:
     }
 };
 
-// ---- data loader (host side; nn/utils/data_loader.hpp:13-92 of the reference) -----------------------------------------------
+// ---- data loader (nn/utils/data_loader.hpp:13-92) ------------------------------------------------------------------------
+// Same file format (little-endian uint32 tokens), same shuffled fixed-length windows and the same order of batches as the
+// reference (std::mt19937_64 + std::shuffle over the sequence indices, reshuffle when fewer than B sequences remain).
+// What differs is where the work happens: a worker thread reads and widens the next batches while the GPU runs the current
+// step, into pinned host blocks that are recycled (the reference seeks, reads and widens on the training thread and pins /
+// unpins the pages of every batch inside to_async, graph/nodes/memory_nodes.hpp:265-317).  A pinned source makes the
+// cudaMemcpyAsync of to_async a real asynchronous copy.
+// GRADC_LOADER_PREFETCH = batches prepared ahead (default 2, 0 = prepare on the calling thread);
+// GRADC_LOADER_PINNED = 0 keeps the blocks in pageable memory.
+class HostBlockPool : public std::enable_shared_from_this<HostBlockPool> {
+    std::mutex m_mu;
+    std::vector<void*> m_free;
+    size_t m_bytes;
+    bool m_pinned;
+
+public:
+    HostBlockPool(size_t bytes, bool pinned) : m_bytes(bytes), m_pinned(pinned) {}
+    HostBlockPool(const HostBlockPool&) = delete;
+    ~HostBlockPool() {
+        for (void* p : m_free) {
+            if (m_pinned) gcb_host_free_pinned(p);
+            else std::free(p);
+        }
+    }
+    // A block that returns to the pool when the last holder lets go of it (the pool lives as long as any block is out).
+    std::shared_ptr<void> take() {
+        void* p = nullptr;
+        {
+            std::lock_guard<std::mutex> g(m_mu);
+            if (!m_free.empty()) { p = m_free.back(); m_free.pop_back(); }
+        }
+        if (!p) {
+            if (m_pinned) gcb_check(gcb_host_alloc_pinned(m_bytes, &p), "pinned batch buffer");
+            else if (posix_memalign(&p, 64, m_bytes ? m_bytes : 64) != 0) throw std::bad_alloc();
+        }
+        std::shared_ptr<HostBlockPool> self = shared_from_this();
+        return std::shared_ptr<void>(p, [self](void* q) { std::lock_guard<std::mutex> g(self->m_mu); self->m_free.push_back(q); });
+    }
+};
+
 class DataLoader {
+    // order state: touched by the worker while it runs, by the caller only while the worker is parked
     std::ifstream m_in;
     int64_t m_total_tokens = 0, m_seq_len = 0, m_total_sequences = 0, m_seq_cursor = 0;
     std::vector<int64_t> m_sequence_indices;
@@ -706,6 +836,92 @@ class DataLoader {
     void shuffle_dataset() {
         std::shuffle(m_sequence_indices.begin(), m_sequence_indices.end(), m_rng);
         m_seq_cursor = 0;
+    }
+
+    struct Snapshot {  // order state before a batch was drawn, to undo batches that were prepared but never handed out
+        int64_t cursor;
+        std::mt19937_64 rng;
+        std::vector<int64_t> indices_before_shuffle;  // filled only when drawing the batch reshuffled
+    };
+    struct Prepared {
+        std::shared_ptr<void> x, y;
+        Snapshot snap;
+    };
+    // prefetch machinery
+    int m_depth = 2;
+    bool m_pinned = true;
+    int64_t m_B = 0;
+    std::shared_ptr<HostBlockPool> m_pool;
+    std::deque<Prepared> m_ready;
+    std::mutex m_mu;
+    std::condition_variable m_cv;
+    std::thread m_worker;
+    bool m_stop = false, m_busy = false;
+    std::exception_ptr m_error;
+
+    // Draws the next batch of m_B sequences into two fresh blocks (reference: data_loader.hpp:56-89).
+    Prepared draw() {
+        Prepared pr;
+        pr.snap.cursor = m_seq_cursor;
+        pr.snap.rng = m_rng;
+        if (m_seq_cursor + m_B > m_total_sequences) {
+            pr.snap.indices_before_shuffle = m_sequence_indices;
+            shuffle_dataset();
+        }
+        pr.x = m_pool->take();
+        pr.y = m_pool->take();
+        int64_t *px = static_cast<int64_t*>(pr.x.get()), *py = static_cast<int64_t*>(pr.y.get());
+        const int64_t T = m_seq_len;
+        std::vector<uint32_t> raw((size_t)T + 1);
+        for (int64_t b = 0; b < m_B; ++b) {
+            const int64_t seq = m_sequence_indices[m_seq_cursor + b];
+            m_in.clear();
+            m_in.seekg(seq * T * (int64_t)sizeof(uint32_t));
+            m_in.read(reinterpret_cast<char*>(raw.data()), (T + 1) * (int64_t)sizeof(uint32_t));
+            if (!m_in) throw std::runtime_error("DataLoader: short read from the dataset file");
+            for (int64_t t = 0; t < T; ++t) { px[b * T + t] = raw[t]; py[b * T + t] = raw[t + 1]; }  // widening uint32 -> int64
+        }
+        m_seq_cursor += m_B;
+        return pr;
+    }
+    void worker_loop() {
+        std::unique_lock<std::mutex> lk(m_mu);
+        for (;;) {
+            m_cv.wait(lk, [&] { return m_stop || ((int)m_ready.size() < m_depth && !m_error); });
+            if (m_stop) return;
+            m_busy = true;
+            lk.unlock();
+            Prepared pr;
+            std::exception_ptr err;
+            try { pr = draw(); } catch (...) { err = std::current_exception(); }
+            lk.lock();
+            m_busy = false;
+            if (err) m_error = err;
+            else m_ready.push_back(std::move(pr));
+            m_cv.notify_all();
+        }
+    }
+    void park_worker() {  // stops and joins the worker; afterwards the order state belongs to the caller
+        {
+            std::lock_guard<std::mutex> g(m_mu);
+            m_stop = true;
+        }
+        m_cv.notify_all();
+        if (m_worker.joinable()) m_worker.join();
+        m_stop = false;
+    }
+    void set_batch_size(int64_t B) {
+        park_worker();
+        if (!m_ready.empty()) {  // undo what was prepared for the old batch size: restore the state before the oldest of them
+            for (auto it = m_ready.rbegin(); it != m_ready.rend(); ++it)
+                if (!it->snap.indices_before_shuffle.empty()) m_sequence_indices = it->snap.indices_before_shuffle;
+            m_seq_cursor = m_ready.front().snap.cursor;
+            m_rng = m_ready.front().snap.rng;
+            m_ready.clear();
+        }
+        m_B = B;
+        m_pool = std::make_shared<HostBlockPool>(sizeof(int64_t) * (size_t)(B * m_seq_len), m_pinned);
+        if (m_depth > 0) m_worker = std::thread([this] { worker_loop(); });
     }
 
 public:
@@ -718,22 +934,34 @@ public:
         m_sequence_indices.resize(m_total_sequences);
         for (int64_t i = 0; i < m_total_sequences; ++i) m_sequence_indices[i] = i;
         shuffle_dataset();
+        if (const char* e = std::getenv("GRADC_LOADER_PREFETCH")) m_depth = std::max(0, std::atoi(e));
+        if (const char* e = std::getenv("GRADC_LOADER_PINNED")) m_pinned = std::atoi(e) != 0;
     }
+    DataLoader(const DataLoader&) = delete;
+    ~DataLoader() { park_worker(); }
     // windows of T+1 little-endian uint32 tokens; X = w[0:T], Y = w[1:T+1], widened to int64
     std::pair<Tensor<int64_t>, Tensor<int64_t>> next_batch(int64_t B, int64_t T, Device cpu_device) {
         if (T != m_seq_len) throw std::invalid_argument("Requested T does not match initialized seq_len.");
-        if (m_seq_cursor + B > m_total_sequences) shuffle_dataset();
-        Tensor<int64_t> X({B, T}, cpu_device, uninitialized), Y({B, T}, cpu_device, uninitialized);
-        int64_t *px = X.data_ptr(), *py = Y.data_ptr();
-        std::vector<uint32_t> raw((size_t)T + 1);
-        for (int64_t b = 0; b < B; ++b) {
-            const int64_t seq = m_sequence_indices[m_seq_cursor + b];
-            m_in.seekg(seq * T * (int64_t)sizeof(uint32_t));
-            m_in.read(reinterpret_cast<char*>(raw.data()), (T + 1) * (int64_t)sizeof(uint32_t));
-            for (int64_t t = 0; t < T; ++t) { px[b * T + t] = raw[t]; py[b * T + t] = raw[t + 1]; }
+        if (B <= 0 || B > m_total_sequences) throw std::invalid_argument("Requested batch size does not fit the dataset.");
+        if (!cpu_device.is_cpu()) throw std::invalid_argument("DataLoader::next_batch produces host tensors; move them with to() / to_async().");
+        if (B != m_B) set_batch_size(B);
+        Prepared pr;
+        if (m_depth == 0) {
+            pr = draw();
+        } else {
+            std::unique_lock<std::mutex> lk(m_mu);
+            m_cv.wait(lk, [&] { return !m_ready.empty() || m_error; });
+            if (m_ready.empty()) std::rethrow_exception(m_error);
+            pr = std::move(m_ready.front());
+            m_ready.pop_front();
+            lk.unlock();
+            m_cv.notify_all();
         }
-        m_seq_cursor += B;
-        return {X, Y};
+        auto make = [&](std::shared_ptr<void> block) {
+            auto st = std::make_shared<Storage<int64_t>>(static_cast<int64_t*>(block.get()), B * T, cpu_device, block);
+            return Tensor<int64_t>(std::vector<int64_t>{B, T}, dense_strides(std::vector<int64_t>{B, T}), 0, std::move(st), false);
+        };
+        return {make(std::move(pr.x)), make(std::move(pr.y))};
     }
     int64_t total_sequences() const { return m_total_sequences; }
 };

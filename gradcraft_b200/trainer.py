@@ -32,6 +32,8 @@ def _lib():
         L.gct_forward_backward.argtypes = [vp, vp, vp, ci, i64, i64, i64, ctypes.POINTER(f32)]
         L.gct_optimizer_step.argtypes = [vp, ctypes.POINTER(f32)]
         L.gct_sync.argtypes = [vp]
+        L.gct_save_checkpoint.argtypes = [vp, ctypes.c_char_p, ctypes.c_char_p]
+        L.gct_load_checkpoint.argtypes = [vp, ctypes.c_char_p, ctypes.c_char_p]
         L.gct_stream.argtypes, L.gct_stream.restype = [vp], vp
         L.gct_context.argtypes, L.gct_context.restype = [vp], vp
         L.gct_dp_init.argtypes = [vp, vp, ci, ci, i64]
@@ -115,6 +117,13 @@ class Trainer:
             tot += l if want_loss else 0.0
         self.optimizer_step()
         return tot
+
+    def save_checkpoint(self, model_path, optim_path):
+        """Weights and AdamW state in the reference's checkpoint file format."""
+        self._ok(self.L.gct_save_checkpoint(self.h, str(model_path).encode(), str(optim_path).encode()))
+
+    def load_checkpoint(self, model_path, optim_path):
+        self._ok(self.L.gct_load_checkpoint(self.h, str(model_path).encode(), str(optim_path).encode()))
 
     def sync(self):
         self._ok(self.L.gct_sync(self.h))

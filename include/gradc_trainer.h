@@ -35,6 +35,10 @@ GCT_API int gct_zero_grad(gct_trainer* tr);
 GCT_API int gct_forward_backward(gct_trainer* tr, const int64_t* tokens, const int64_t* targets, int on_device, int64_t B, int64_t T, int64_t accum, float* loss_out);
 /* clip (if enabled) + AdamW.  norm_out may be NULL. */
 GCT_API int gct_optimizer_step(gct_trainer* tr, float* norm_out);
+/* Model weights and AdamW state (moments + beta powers) to / from files in the reference's checkpoint format
+ * (nn/utils/checkpoint.hpp:12-77; train.cpp:174-179 and :100-118).  Arena-resident state moves as one copy per array. */
+GCT_API int gct_save_checkpoint(gct_trainer* tr, const char* model_path, const char* optim_path);
+GCT_API int gct_load_checkpoint(gct_trainer* tr, const char* model_path, const char* optim_path);
 GCT_API int gct_sync(gct_trainer* tr);
 GCT_API void* gct_stream(gct_trainer* tr);           /* cudaStream_t the step runs on */
 GCT_API void* gct_context(gct_trainer* tr);          /* gcb_ctx* of include/gradc_b200.h */

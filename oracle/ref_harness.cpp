@@ -21,12 +21,16 @@
 //        Writes <outprefix>_loss.txt, _grads<k>.ckpt and _weights<k>.ckpt for k in {1, steps}, _time.txt.
 //   ref_harness ops  in.ckpt out.ckpt
 //        Runs every op-level case whose inputs are present in in.ckpt (see run_ops()).
+//   ref_harness loader dataset.bin T n_batches B1 [B2 switch_at]
+//        The reference's DataLoader (nn/utils/data_loader.hpp:13-92, seed 67 as train.cpp:77): one line per batch with the
+//        batch size and an FNV-1a hash of inputs and targets.
 //   ref_harness gptcuda <arch> V T C H L F B steps warmup tokens.i64        (only in the build that links the reference's .cu files)
 //        Times the reference's CUDA path the way train.cpp:136-161 drives it: model.to(gpu), softmax_crossentropy_fast,
 //        clip, AdamW fast branch; prints one line "tokens_per_s <v> ms_per_step <t> hwm_gb <g> loss <l>".
 #include "gradc/gradc.hpp"
 
 #include <chrono>
+#include <cstdio>
 #include <cstring>
 #include <fstream>
 #include <iostream>
@@ -412,6 +416,23 @@ int main(int argc, char** argv) {
             }
             std::cerr << "unknown arch " << arch << "\n";
             return 2;
+        }
+        if (mode == "loader") {
+            if (argc < 6) { std::cerr << "usage: ref_harness loader dataset.bin T n_batches B1 [B2 switch_at]\n"; return 2; }
+            const int64_t T = std::stoll(argv[3]), n = std::stoll(argv[4]), B1 = std::stoll(argv[5]);
+            const int64_t B2 = argc > 7 ? std::stoll(argv[6]) : B1, sw = argc > 7 ? std::stoll(argv[7]) : n;
+            DataLoader loader(argv[2], T, 67);
+            auto fnv = [](const int64_t* p, int64_t cnt) {
+                unsigned long long h = 1469598103934665603ull;
+                for (int64_t i = 0; i < cnt; ++i) { h ^= (unsigned long long)p[i]; h *= 1099511628211ull; }
+                return h;
+            };
+            for (int64_t i = 0; i < n; ++i) {
+                const int64_t B = i < sw ? B1 : B2;
+                auto [X, Y] = loader.next_batch(B, T, Device(DeviceType::CPU));
+                std::printf("%lld %llu %llu\n", (long long)B, fnv(X._get_storage()->data(), B * T), fnv(Y._get_storage()->data(), B * T));
+            }
+            return 0;
         }
         if (mode == "gptcuda") {
             if (argc != 13) { std::cerr << "usage: ref_harness gptcuda arch V T C H L F B steps warmup tokens\n"; return 2; }

@@ -89,10 +89,36 @@ def run_gpt(tmp, name):
     print(name, "loss", out["loss"])
 
 
+# The reference DataLoader's batch order on a seeded dataset.bin: (dataset seed, tokens, vocab, T, n_batches, B1, B2, switch_at)
+LOADER_CASES = {"plain": (5, 20 * 33 + 7, 997, 32, 12, 3, 3, 12), "switch": (5, 20 * 33 + 7, 997, 32, 12, 3, 5, 5)}
+
+
+def loader_dataset(path, seed, n_tokens, vocab):
+    synth.zipf_tokens(seed, n_tokens, vocab).astype("<u4").tofile(path)
+
+
+def run_loader(tmp):
+    lines = {}
+    for name, (seed, n_tok, vocab, T, n, b1, b2, sw) in LOADER_CASES.items():
+        path = os.path.join(tmp, "dataset_%s.bin" % name)
+        loader_dataset(path, seed, n_tok, vocab)
+        r = subprocess.run([HARNESS, "loader", path, str(T), str(n), str(b1), str(b2), str(sw)], capture_output=True, text=True, check=True)
+        lines[name] = r.stdout.strip()
+    with open(os.path.join(HERE, "loader_order.txt"), "w") as f:
+        for name, text in lines.items():
+            f.write("# %s\n%s\n" % (name, text))
+    print("loader_order.txt written")
+
+
 if __name__ == "__main__":
+    if "--loader-only" in sys.argv:
+        with tempfile.TemporaryDirectory() as tmp:
+            run_loader(tmp)
+        sys.exit(0)
     if not os.path.exists(HARNESS):
         sys.exit("oracle/_ref/ref_harness missing: run oracle/build_ref.sh first")
     with tempfile.TemporaryDirectory() as tmp:
         run_ops(tmp)
         for name in GPT_CASES:
             run_gpt(tmp, name)
+        run_loader(tmp)
