@@ -272,15 +272,38 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) norm_bwd_ring(float* __res
     }
 }
 
+// Second stage of dgamma / dbeta: sums the per-CTA partial rows in a fixed order.  A block covers 32 of the 2 * cols
+// outputs; its 8 thread groups take the partial rows k = g, g + 8, ... (four independent accumulators each, so the loads
+// overlap), and the 8 group sums are added in group order.
 __global__ void __launch_bounds__(256) norm_params_stage2(float* __restrict__ dgamma, float* __restrict__ dbeta, const float* __restrict__ partial, int nparts, int cols, int accumulate) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;  // over 2 * cols
-    if (i >= 2 * cols) return;
-    float* dst = (i < cols) ? dgamma : dbeta;
-    if (dst == nullptr) return;
-    float s = 0.0f;
-    for (int k = 0; k < nparts; ++k) s += partial[(size_t)k * 2 * cols + i];
-    const int c = (i < cols) ? i : i - cols;
-    dst[c] = accumulate ? dst[c] + s : s;
+    __shared__ float red[8][33];
+    const int lane_c = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + lane_c;  // over 2 * cols
+    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    if (i < 2 * cols) {
+        const float* p = partial + i;
+        const size_t stride = (size_t)2 * cols;
+        int k = g;
+        for (; k + 24 < nparts; k += 32) {
+            a0 += p[(size_t)k * stride];
+            a1 += p[(size_t)(k + 8) * stride];
+            a2 += p[(size_t)(k + 16) * stride];
+            a3 += p[(size_t)(k + 24) * stride];
+        }
+        for (; k < nparts; k += 8) a0 += p[(size_t)k * stride];
+    }
+    red[g][lane_c] = (a0 + a1) + (a2 + a3);
+    __syncthreads();
+    if (g == 0 && i < 2 * cols) {
+        float s = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) s += red[q][lane_c];
+        float* dst = (i < cols) ? dgamma : dbeta;
+        if (dst != nullptr) {
+            const int c = (i < cols) ? i : i - cols;
+            dst[c] = accumulate ? dst[c] + s : s;
+        }
+    }
 }
 
 // ---- generic shapes: CTA per row ---------------------------------------------------------------
@@ -421,7 +444,7 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
         int rc = after_launch(ctx, name);
         if (rc) return rc;
         if (want_params) {
-            norm_params_stage2<<<(unsigned)((2 * cols + 255) / 256), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params);
+            norm_params_stage2<<<(unsigned)((2 * cols + 31) / 32), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params);
             rc = after_launch(ctx, name);
         }
         return rc;
@@ -439,7 +462,7 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
         int rc = after_launch(ctx, name);
         if (rc) return rc;
         if (want_params) {
-            norm_params_stage2<<<(unsigned)((2 * cols + 255) / 256), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params);
+            norm_params_stage2<<<(unsigned)((2 * cols + 31) / 32), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params);
             rc = after_launch(ctx, name);
         }
         return rc;
@@ -463,7 +486,7 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
         norm_bwd_params_block<IS_LN><<<grid, 256, 0, ctx->stream>>>(sc.as<float>(), dy, x, s0, s1, rows, cols, rps);
         rc = after_launch(ctx, name);
         if (rc) return rc;
-        norm_params_stage2<<<(unsigned)((2 * cols + 255) / 256), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)slabs, (int)cols, acc_params);
+        norm_params_stage2<<<(unsigned)((2 * cols + 31) / 32), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)slabs, (int)cols, acc_params);
         return after_launch(ctx, name);
     }
     return GCB_OK;
@@ -524,7 +547,7 @@ int gcb_layernorm_bwd_noalloc_f32(gcb_ctx* ctx, float* dx, float* dgamma, float*
     rc = after_launch(ctx, "layernorm_bwd_noalloc");
     if (rc) return rc;
     if (want_params) {
-        norm_params_stage2<<<(unsigned)((2 * cols + 255) / 256), 256, 0, ctx->stream>>>(dgamma, dbeta, scratch, (int)blocks, (int)cols, acc_params);
+        norm_params_stage2<<<(unsigned)((2 * cols + 31) / 32), 256, 0, ctx->stream>>>(dgamma, dbeta, scratch, (int)blocks, (int)cols, acc_params);
         rc = after_launch(ctx, "layernorm_bwd_noalloc");
     }
     return rc;
