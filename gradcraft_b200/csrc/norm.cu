@@ -77,6 +77,7 @@ template <int NCHUNK, bool IS_LN>
 __global__ void __launch_bounds__(kNormWarps * 32) norm_bwd_warp(float* __restrict__ dx, float* __restrict__ partial, const float* __restrict__ dy, const float* __restrict__ x,
                                                                  const float* __restrict__ gamma, const float* __restrict__ stat0, const float* __restrict__ stat1,
                                                                  int64_t rows, int cols, int acc_dx, int want_params) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the second stage (if any) may be scheduled while this grid drains; it still waits for this grid to complete
     extern __shared__ float sm[];  // [kNormWarps][2][cols]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int64_t warp = (int64_t)blockIdx.x * kNormWarps + wid;
@@ -176,6 +177,7 @@ template <int NCHUNK, bool IS_LN>
 __global__ void __launch_bounds__(kRingWarps * 32, 1) norm_bwd_ring(float* __restrict__ dx, float* __restrict__ partial, const float* __restrict__ dy, const float* __restrict__ x,
                                                                     const float* __restrict__ gamma, const float* __restrict__ stat0, const float* __restrict__ stat1, int64_t rows, int cols,
                                                                     int acc_dx, int want_params, int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the second stage (if any) may be scheduled while this grid drains; it still waits for this grid to complete
     extern __shared__ __align__(128) uint8_t ring_smem[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const uint32_t row_bytes = (uint32_t)cols * 4u;
@@ -279,6 +281,9 @@ __global__ void __launch_bounds__(256) norm_params_stage2(float* __restrict__ dg
     __shared__ float red[8][33];
     const int lane_c = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int i = blockIdx.x * 32 + lane_c;  // over 2 * cols
+    // launched with programmatic stream serialisation: this grid may start while the kernel that writes `partial` drains;
+    // nothing of it is read before that kernel has completed and its writes are visible
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
     if (i < 2 * cols) {
         const float* p = partial + i;
@@ -304,6 +309,21 @@ __global__ void __launch_bounds__(256) norm_params_stage2(float* __restrict__ dg
             dst[c] = accumulate ? dst[c] + s : s;
         }
     }
+}
+
+// Launches the second stage so that its blocks are scheduled while the first stage's last blocks finish (the gap between
+// two dependent launches is a tenth of this backward at 16k x 1k).
+static cudaError_t launch_params_stage2(cudaStream_t stream, float* dgamma, float* dbeta, const float* partial, int nparts, int cols, int accumulate) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((2 * cols + 31) / 32), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, norm_params_stage2, dgamma, dbeta, partial, nparts, cols, accumulate);
 }
 
 // ---- generic shapes: CTA per row ---------------------------------------------------------------
@@ -444,7 +464,7 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
         int rc = after_launch(ctx, name);
         if (rc) return rc;
         if (want_params) {
-            norm_params_stage2<<<(unsigned)((2 * cols + 31) / 32), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params);
+            GCB_CHECK_CUDA(launch_params_stage2(ctx->stream, dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params));
             rc = after_launch(ctx, name);
         }
         return rc;
@@ -462,7 +482,7 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
         int rc = after_launch(ctx, name);
         if (rc) return rc;
         if (want_params) {
-            norm_params_stage2<<<(unsigned)((2 * cols + 31) / 32), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params);
+            GCB_CHECK_CUDA(launch_params_stage2(ctx->stream, dgamma, dbeta, sc.as<float>(), (int)blocks, (int)cols, acc_params));
             rc = after_launch(ctx, name);
         }
         return rc;
@@ -486,7 +506,7 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
         norm_bwd_params_block<IS_LN><<<grid, 256, 0, ctx->stream>>>(sc.as<float>(), dy, x, s0, s1, rows, cols, rps);
         rc = after_launch(ctx, name);
         if (rc) return rc;
-        norm_params_stage2<<<(unsigned)((2 * cols + 31) / 32), 256, 0, ctx->stream>>>(dgamma, dbeta, sc.as<float>(), (int)slabs, (int)cols, acc_params);
+        GCB_CHECK_CUDA(launch_params_stage2(ctx->stream, dgamma, dbeta, sc.as<float>(), (int)slabs, (int)cols, acc_params));
         return after_launch(ctx, name);
     }
     return GCB_OK;
@@ -547,7 +567,7 @@ int gcb_layernorm_bwd_noalloc_f32(gcb_ctx* ctx, float* dx, float* dgamma, float*
     rc = after_launch(ctx, "layernorm_bwd_noalloc");
     if (rc) return rc;
     if (want_params) {
-        norm_params_stage2<<<(unsigned)((2 * cols + 31) / 32), 256, 0, ctx->stream>>>(dgamma, dbeta, scratch, (int)blocks, (int)cols, acc_params);
+        GCB_CHECK_CUDA(launch_params_stage2(ctx->stream, dgamma, dbeta, scratch, (int)blocks, (int)cols, acc_params));
         rc = after_launch(ctx, "layernorm_bwd_noalloc");
     }
     return rc;
