@@ -101,6 +101,25 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
 // streaming variants: data touched once should not evict what the next kernel wants from L2/L1
+// tanh-approximation GELU and its derivative (reference: backend/cuda/math_functors.cuh:184-214, 425-443), shared by the
+// elementwise kernels and the GEMM epilogue that applies the derivative
+__device__ __forceinline__ float fast_tanh(float u) {
+    // tanh(u) = 1 - 2 / (1 + e^{2u}); ex2.approx + rcp.approx keep the absolute error near 1e-7,
+    // and the form saturates cleanly to +-1 for large |u|.
+    const float e = __expf(2.0f * u);
+    return 1.0f - __fdividef(2.0f, 1.0f + e);
+}
+__device__ __forceinline__ float gelu_f(float x) {
+    const float a = 0.7978845608f, b = 0.044715f;
+    return x * 0.5f * (1.0f + fast_tanh(a * (x + b * x * x * x)));
+}
+__device__ __forceinline__ float gelu_grad_f(float x) {
+    const float a = 0.7978845608f, b = 0.044715f;
+    const float x2 = x * x;
+    const float t = fast_tanh(a * (x + b * x2 * x));
+    const float up = a * (1.0f + 3.0f * b * x2);
+    return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * up;
+}
 __device__ __forceinline__ float4 ld4_stream(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
 __device__ __forceinline__ void st4_stream(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
 

@@ -72,23 +72,6 @@ static int ew_launch(gcb_ctx* ctx, const char* name, EwPtrs<NIN, NOUT> p, int64_
 }
 
 // ---- functors ------------------------------------------------------------------------------------
-__device__ __forceinline__ float fast_tanh(float u) {
-    // tanh(u) = 1 - 2 / (1 + e^{2u}); ex2.approx + rcp.approx keep the absolute error near 1e-7,
-    // and the form saturates cleanly to +-1 for large |u|.
-    const float e = __expf(2.0f * u);
-    return 1.0f - __fdividef(2.0f, 1.0f + e);
-}
-__device__ __forceinline__ float gelu_f(float x) {
-    const float a = 0.7978845608f, b = 0.044715f;
-    return x * 0.5f * (1.0f + fast_tanh(a * (x + b * x * x * x)));
-}
-__device__ __forceinline__ float gelu_grad_f(float x) {
-    const float a = 0.7978845608f, b = 0.044715f;
-    const float x2 = x * x;
-    const float t = fast_tanh(a * (x + b * x2 * x));
-    const float up = a * (1.0f + 3.0f * b * x2);
-    return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * up;
-}
 __device__ __forceinline__ float sigmoid_f(float a) { return __fdividef(1.0f, 1.0f + __expf(-a)); }
 
 struct UnaryOp {

@@ -25,6 +25,17 @@ static int run_gemm(gcb_ctx* ctx, int op_a, int op_b, const GemmArgs& g, const c
     }
     int rc = GCB_UNSUPPORTED;
     if (ctx->gemm_engine != 1 && gemm_tc_eligible(ta, tb, g)) rc = gemm_tc_launch(ctx, ta, tb, g);
+    if (rc == GCB_UNSUPPORTED && (g.gelu_pre || g.gelu_act)) {
+        // no kernel with the fused GELU epilogues takes this problem: the same product, then the elementwise pass over C
+        GemmArgs plain = g;
+        plain.gelu_pre = nullptr;
+        plain.gelu_act = nullptr;
+        rc = run_gemm(ctx, op_a, op_b, plain, who);
+        if (rc == GCB_OK && g.gelu_pre) rc = gcb_gelu_bwd_f32(ctx, g.C, g.C, g.gelu_pre, g.M * g.N, 0);
+        if (rc == GCB_OK && g.gelu_act) rc = gcb_gelu_fwd_f32(ctx, g.gelu_act, g.C, g.M * g.N);
+        if (e1) GCB_CHECK_CUDA(cudaEventRecord(e1, ctx->stream));
+        return rc;
+    }
     if (rc == GCB_UNSUPPORTED) {
         if (ctx->gemm_engine == 2) {
             set_error("%s: the tcgen05 engine was forced but cannot take these operands (alignment / leading dimensions)", who);
@@ -77,6 +88,24 @@ int gcb_gemm_batched_softmax_bwd_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M
     g.causal = 1;
     g.sm_probs = probs; g.sm_rowdot = row_dot; g.sm_scale = scale;
     return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_batched_softmax_bwd_f32");
+}
+
+int gcb_gemm_gelu_bwd_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B, int64_t ldb, const float* pre, float* dpre) {
+    GCB_REQUIRE(ctx, "gcb_gemm_gelu_bwd_f32: ctx is NULL");
+    GCB_REQUIRE(M == 0 || N == 0 || (pre && dpre), "gcb_gemm_gelu_bwd_f32: NULL pre / dpre");
+    GCB_REQUIRE(pre != dpre, "gcb_gemm_gelu_bwd_f32: dpre must not alias pre");
+    GemmArgs g{M, N, K, 1.0f, 0.0f, A, B, nullptr, dpre, lda, ldb, N, 0, 0, 0, 0, 0, 0, 1, 1};
+    g.gelu_pre = pre;
+    return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_gelu_bwd_f32");
+}
+
+int gcb_linear_gelu_fwd_f32(gcb_ctx* ctx, int op_b, int64_t M, int64_t N, int64_t K, const float* x, int64_t lda, const float* W, int64_t ldb, const float* bias, float* pre, float* act) {
+    GCB_REQUIRE(ctx, "gcb_linear_gelu_fwd_f32: ctx is NULL");
+    GCB_REQUIRE(M == 0 || N == 0 || (pre && act), "gcb_linear_gelu_fwd_f32: NULL pre / act");
+    GCB_REQUIRE(pre != act, "gcb_linear_gelu_fwd_f32: act must not alias pre");
+    GemmArgs g{M, N, K, 1.0f, 0.0f, x, W, bias, pre, lda, ldb, N, 0, 0, 0, 0, 0, 0, 1, 1};
+    g.gelu_act = act;
+    return run_gemm(ctx, GCB_OP_N, op_b, g, "gcb_linear_gelu_fwd_f32");
 }
 
 int gcb_profile_gemm_begin(gcb_ctx* ctx) {

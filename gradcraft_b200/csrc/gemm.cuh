@@ -15,6 +15,10 @@ struct GemmArgs {
     int causal = 0;  // 0 none; 1 output needed on/below the diagonal only; 2 op(A)[m,k] = 0 for k > m; 3 op(A)[m,k] = 0 for k < m
     // softmax-backward epilogue (needs causal == 1): C[m,n] = sm_scale * sm_probs[m,n] * (alpha * (op(A) op(B))[m,n] - sm_rowdot[m]) for n <= m, 0 for n > m.
     // sm_probs is laid out like C; sm_rowdot holds M values per batch item, batch items in (outer, inner) order.
+    // GELU-backward epilogue (needs beta == 0): C[m,n] = (alpha * (op(A) op(B))[m,n] + bias[n]) * gelu'(gelu_pre[m,n]); gelu_pre is laid out like C
+    const float* gelu_pre = nullptr;
+    // GELU-forward epilogue: besides C, gelu(C[m,n]) is written to gelu_act, laid out like C
+    float* gelu_act = nullptr;
     const float* sm_probs = nullptr;
     const float* sm_rowdot = nullptr;
     float sm_scale = 1.0f;

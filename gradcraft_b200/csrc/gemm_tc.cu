@@ -52,6 +52,8 @@ struct TcParams {
                          // 1: three TF32 products; big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
                          // 0: as 1 with big = rna_tf32(x) written back, small = x - big (does not rely on the hardware's truncation)
     float* partial;      // [splits][M][N] when splits > 1
+    const float* gelu_pre;   // GELU-backward epilogue (see GemmArgs), or NULL: applied by the pair kernel only
+    float* gelu_act;         // GELU-forward second output (see GemmArgs), or NULL: pair kernel only
     const float* sm_probs;   // softmax-backward epilogue (see GemmArgs), or NULL
     const float* sm_rowdot;
     float sm_scale;
@@ -906,18 +908,35 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
             const TileCoord tc = pair_tile_coord(p, w);
             if (tc.skip) continue;
             const uint32_t buf = lt % NACC;
-            ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt / NACC) & 1u, p.status, 14)) != 0;
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float* cbase = to_partial ? p.partial + (int64_t)tc.split * p.M * p.N : p.C + (int64_t)tc.b_out * p.c_so + (int64_t)tc.b_in * p.c_si;
             const int64_t ld = to_partial ? p.N : p.ldc;
             const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
             const float* bias = to_partial ? nullptr : p.bias;
+            const float* gelu_pre = to_partial ? nullptr : p.gelu_pre;
+            float* gelu_act = to_partial ? nullptr : p.gelu_act;
             const int64_t mrow0 = (int64_t)tc.m0 + 128 * (int)rank + 32 * q;
+            if (gelu_pre) {  // pull this warp's part of the pre-activation tile into L2 while the tile's MMAs are still running
+                const int64_t col0 = (int64_t)tc.n0 + 32 * c_begin;
+                const int lines = (int)max((int64_t)0, (min(p.N, (int64_t)tc.n0 + 32 * c_end) - col0 + 31) / 32);
+                for (int i = lane; i < 32 * lines; i += 32) {
+                    const int64_t r = mrow0 + i / lines;
+                    if (r < p.M) asm volatile("prefetch.global.L2 [%0];" ::"l"(gelu_pre + (cbase - p.C) + r * ld + col0 + 32 * (i % lines)));
+                }
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt / NACC) & 1u, p.status, 14)) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c = c_begin; c < c_end; ++c) {
                 const int64_t nb = (int64_t)tc.n0 + 32 * c;
                 if (nb >= p.N) break;
+                const bool blk_fast = vec_ok && mrow0 + 32 <= p.M && nb + 32 <= p.N;  // whole 32 x 32 block in bounds
+                float4 gp[8];  // GELU-backward epilogue: the block's pre-activations are requested before the accumulator is read
+                if (gelu_pre && blk_fast) {
+                    const float* pp = gelu_pre + (cbase - p.C) + (mrow0 + sub_r) * ld + nb + sub_c;
+#pragma unroll
+                    for (int r4 = 0; r4 < 8; ++r4) gp[r4] = ld4(pp + (int64_t)r4 * 4 * ld);
+                }
                 float v[32];
                 tmem_ld32(tmem_base + buf * BN + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), v);
 #pragma unroll
@@ -927,7 +946,7 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                     const int64_t m_first = mrow0 + sub_r, n = nb + sub_c;
                     float* dst = cbase + m_first * ld + n;
                     const float* src = stg + sub_r * S::EPI_PITCH + sub_c;
-                    if (vec_ok && mrow0 + 32 <= p.M && nb + 32 <= p.N) {  // whole 32 x 32 block in bounds: pointer-increment fast path
+                    if (blk_fast) {  // pointer-increment fast path
                         float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (bias) bb = bias_vec ? __ldg(reinterpret_cast<const float4*>(bias + n)) : make_float4(bias[n], bias[n + 1], bias[n + 2], bias[n + 3]);
                         const int64_t step = 4 * ld;
@@ -936,7 +955,9 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                             float4 o = *reinterpret_cast<const float4*>(src);
                             o.x = fmaf(o.x, alpha, bb.x); o.y = fmaf(o.y, alpha, bb.y); o.z = fmaf(o.z, alpha, bb.z); o.w = fmaf(o.w, alpha, bb.w);
                             if (beta != 0.0f) { const float4 old = ld4(dst); o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y); o.z = fmaf(beta, old.z, o.z); o.w = fmaf(beta, old.w, o.w); }
+                            if (gelu_pre) { o.x *= gelu_grad_f(gp[r4].x); o.y *= gelu_grad_f(gp[r4].y); o.z *= gelu_grad_f(gp[r4].z); o.w *= gelu_grad_f(gp[r4].w); }
                             st4(dst, o);
+                            if (gelu_act) st4(gelu_act + (dst - p.C), make_float4(gelu_f(o.x), gelu_f(o.y), gelu_f(o.z), gelu_f(o.w)));
                         }
                     } else {
                         for (int r4 = 0; r4 < 8; ++r4) {
@@ -949,7 +970,9 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                                     float r = sp[u] * alpha;
                                     if (bias) r += bias[n + u];
                                     if (beta != 0.0f) r += beta * d[u];
+                                    if (gelu_pre) r *= gelu_grad_f(gelu_pre[(d - p.C) + u]);
                                     d[u] = r;
+                                    if (gelu_act) gelu_act[(d - p.C) + u] = gelu_f(r);
                                 }
                             }
                         }
@@ -1128,12 +1151,14 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     p.k_blocks_total = (int)((g.K + TC_BK - 1) / TC_BK);
     p.status = ctx->d_status;
     p.sm_probs = g.sm_probs; p.sm_rowdot = g.sm_rowdot; p.sm_scale = g.sm_scale;
+    p.gelu_pre = g.gelu_pre; p.gelu_act = g.gelu_act;
+    if ((g.gelu_pre || g.gelu_act) && !use_pair) return GCB_UNSUPPORTED;  // only the pair kernel carries this epilogue; the caller applies it as a second pass instead
     const int64_t tiles = (int64_t)p.tiles_n * p.tiles_m * batches;
     if (tiles > 2147483647LL / 2) return GCB_UNSUPPORTED;
     // split-K when the tiles alone would leave SMs idle: pick the slice count with the lowest modelled time
     // (rounds of 148 persistent CTAs x K blocks per slice, plus writing and re-reading the partial tiles)
     int splits = 1;
-    if (batches == 1 && p.k_blocks_total >= 64 && g.causal == 0) {
+    if (batches == 1 && p.k_blocks_total >= 64 && g.causal == 0 && !g.gelu_pre && !g.gelu_act) {
         const int ctas = use_pair ? kSMs / 2 : kSMs * (BN == 64 ? 2 : 1);
         double best = 1e30;
         for (int sp = 1; sp <= 32 && p.k_blocks_total / sp >= 16; ++sp) {

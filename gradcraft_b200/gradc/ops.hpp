@@ -377,13 +377,7 @@ class GeLUNode : public Node<float> {
 
 public:
     explicit GeLUNode(Tensor<float> p) : m_parent(std::move(p)) {}
-    Tensor<float> realize() override {
-        m_parent.realize();
-        m_parent = Tensor<float>(make_contiguous(m_parent));
-        Tensor<float> out(m_parent.shape(), m_parent.device(), uninitialized);
-        gcb_check(gcb_gelu_fwd_f32(ctx_of(out), out.data_ptr(), m_parent.data_ptr(), out.volume()), "gelu");
-        return out;
-    }
+    Tensor<float> realize() override;  // defined after MatMulNode: a linear layer that feeds only this node computes both values in one GEMM
     void backward(const Tensor<float>& g, bool) override {
         if (!m_parent.requires_grad()) return;
         Tensor<float> gc = make_contiguous(g);
@@ -391,6 +385,7 @@ public:
         gcb_check(gcb_gelu_bwd_f32(ctx_of(gc), dst.data_ptr(), gc.data_ptr(), m_parent.data_ptr(), gc.volume(), acc ? 1 : 0), "gelu backward");
     }
     std::vector<TensorStateBase*> get_input_states() override { return {m_parent._get_state_base()}; }
+    const Tensor<float>& parent() const { return m_parent; }
 };
 template <typename T>
 Tensor<T> Tensor<T>::gelu() const requires std::is_floating_point_v<T> {
@@ -533,7 +528,9 @@ class MatMulNode : public Node<float> {
 public:
     MatMulNode(Tensor<float> x, Tensor<float> w, Tensor<float> b, int64_t M, int64_t K, int64_t N, std::vector<int64_t> out_shape)
         : m_x(std::move(x)), m_w(std::move(w)), m_b(std::move(b)), m_M(M), m_K(K), m_N(N), m_out_shape(std::move(out_shape)) {}
-    Tensor<float> realize() override {
+    Tensor<float> realize() override { return realize_impl(nullptr); }
+    // y = x W + b, and gelu(y) into *gelu_out (allocated here) when that is asked for: one GEMM with two outputs
+    Tensor<float> realize_impl(Tensor<float>* gelu_out) {
         m_x.realize();
         m_w.realize();
         const bool has_bias = m_b._get_state() != nullptr;
@@ -541,6 +538,12 @@ public:
         MatView w;
         if (!as_matview(m_w, w)) throw std::runtime_error("matmul: the right operand must be a (possibly transposed) matrix view");
         Tensor<float> out(m_out_shape, m_x.device(), uninitialized);
+        if (gelu_out != nullptr) {
+            *gelu_out = Tensor<float>(m_out_shape, m_x.device(), uninitialized);
+            gcb_check(gcb_linear_gelu_fwd_f32(ctx_of(out), w.transposed ? GCB_OP_T : GCB_OP_N, m_M, m_N, m_K, m_x.data_ptr(), m_K, w.p, w.ld, has_bias ? m_b.data_ptr() : nullptr, out.data_ptr(),
+                                              gelu_out->data_ptr()), "linear + gelu");
+            return out;
+        }
         gcb_check(gcb_gemm_f32(ctx_of(out), GCB_OP_N, w.transposed ? GCB_OP_T : GCB_OP_N, m_M, m_N, m_K, 1.0f, m_x.data_ptr(), m_K, w.p, w.ld, 0.0f, out.data_ptr(), m_N,
                                has_bias ? m_b.data_ptr() : nullptr), "matmul");
         return out;
@@ -551,8 +554,22 @@ public:
         MatView w;
         as_matview(m_w, w);
         if (m_x.requires_grad()) {  // dX[M,K] = dY[M,N] . W^T
-            auto [dx, acc] = m_x.grad_target();
-            gcb_check(gcb_gemm_f32(c, GCB_OP_N, w.transposed ? GCB_OP_N : GCB_OP_T, m_M, m_K, m_N, 1.0f, gc.data_ptr(), m_N, w.p, w.ld, acc ? 1.0f : 0.0f, dx.data_ptr(), m_K, nullptr), "matmul dX");
+            // x = gelu(pre): the GEMM applies gelu'(pre) in its epilogue and hands the result to pre directly; x itself then
+            // receives no gradient here, so the sweep skips the GELU node (any other consumer of x still goes through it)
+            bool fused = false;
+            auto* gn = dynamic_cast<GeLUNode*>(m_x._get_state()->m_creation_op.get());
+            if (gn != nullptr && gn->parent().requires_grad() && gn->parent().is_contiguous() && gn->parent().volume() == m_M * m_K && !m_x._get_state()->m_grad.has_value()) {
+                Tensor<float> pre = gn->parent();
+                auto [dpre, acc] = pre.grad_target();
+                if (!acc) {
+                    gcb_check(gcb_gemm_gelu_bwd_f32(c, GCB_OP_N, w.transposed ? GCB_OP_N : GCB_OP_T, m_M, m_K, m_N, gc.data_ptr(), m_N, w.p, w.ld, pre.data_ptr(), dpre.data_ptr()), "matmul dX with GELU backward");
+                    fused = true;
+                }
+            }
+            if (!fused) {
+                auto [dx, acc] = m_x.grad_target();
+                gcb_check(gcb_gemm_f32(c, GCB_OP_N, w.transposed ? GCB_OP_N : GCB_OP_T, m_M, m_K, m_N, 1.0f, gc.data_ptr(), m_N, w.p, w.ld, acc ? 1.0f : 0.0f, dx.data_ptr(), m_K, nullptr), "matmul dX");
+            }
         }
         if (m_w.requires_grad()) {
             // A transposed view of a matrix E (the tied head): write dE[N,K] = dY^T . X straight into E's gradient, so neither
@@ -581,6 +598,21 @@ public:
         return v;
     }
 };
+
+inline Tensor<float> GeLUNode::realize() {
+    auto st = m_parent._get_state();
+    auto* mm = dynamic_cast<MatMulNode*>(st->m_creation_op.get());
+    if (mm != nullptr && !st->m_is_realized && m_parent.is_contiguous() && m_parent.offset() == 0) {
+        Tensor<float> out;
+        m_parent.adopt_result(mm->realize_impl(&out));
+        return out;
+    }
+    m_parent.realize();
+    m_parent = Tensor<float>(make_contiguous(m_parent));
+    Tensor<float> out(m_parent.shape(), m_parent.device(), uninitialized);
+    gcb_check(gcb_gelu_fwd_f32(ctx_of(out), out.data_ptr(), m_parent.data_ptr(), out.volume()), "gelu");
+    return out;
+}
 
 inline Tensor<float> linear(Tensor<float> x, Tensor<float> w, Tensor<float> b) {
     Device d = infer_assert_device(x, w);

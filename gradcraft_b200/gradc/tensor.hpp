@@ -282,6 +282,9 @@ public:
 
     // graph
     void realize();
+    // Installs the value a node computed for this (so far lazy) tensor — what realize() does with its node's result; for a
+    // consumer node that computed its parent's value together with its own.
+    void adopt_result(Tensor computed);
     void backward(bool retain_graph = false);
     void zero_grad();
     bool is_exclusive() const { return m_state.use_count() == 1 && m_state->m_storage.use_count() == 1; }
@@ -378,15 +381,21 @@ public:
 };
 
 template <typename T>
+void Tensor<T>::adopt_result(Tensor computed) {
+    if (m_state->m_storage != computed.m_state->m_storage) {
+        // every alias of this state sees the result: swap the payload of the shared Storage object
+        std::swap(m_state->m_storage->m_data, computed.m_state->m_storage->m_data);
+        std::swap(m_state->m_storage->m_owner, computed.m_state->m_storage->m_owner);
+        if (m_state->m_storage->m_size != computed.m_state->m_storage->m_size) std::swap(m_state->m_storage->m_size, computed.m_state->m_storage->m_size);
+    }
+    m_state->m_is_realized = true;
+}
+
+template <typename T>
 void Tensor<T>::realize() {
     if (m_state->m_creation_op != nullptr && !m_state->m_is_realized) {
-        Tensor computed = m_state->m_creation_op->realize();
-        if (m_state->m_storage != computed.m_state->m_storage) {
-            // every alias of this state sees the result: swap the payload of the shared Storage object
-            std::swap(m_state->m_storage->m_data, computed.m_state->m_storage->m_data);
-            std::swap(m_state->m_storage->m_owner, computed.m_state->m_storage->m_owner);
-            if (m_state->m_storage->m_size != computed.m_state->m_storage->m_size) std::swap(m_state->m_storage->m_size, computed.m_state->m_storage->m_size);
-        }
+        adopt_result(m_state->m_creation_op->realize());
+        return;
     }
     m_state->m_is_realized = true;
 }

@@ -167,6 +167,17 @@ GCB_API int gcb_gemm_batched_softmax_bwd_f32(gcb_ctx* ctx, int op_a, int op_b, i
                                      float* dscores, int64_t ldc, int64_t c_stride_outer, int64_t c_stride_inner,
                                      int64_t batch_outer, int64_t batch_inner, const float* probs, const float* row_dot, float scale);
 
+/* pre = x op(W) + bias and act = gelu(pre) from one GEMM (both M x N, dense): Linear::forward (nn/layers/linear.hpp:22-25)
+ * followed by Tensor::gelu() (graph/nodes/activation_nodes.hpp:157-192); pre is kept because the GELU backward needs it. */
+GCB_API int gcb_linear_gelu_fwd_f32(gcb_ctx* ctx, int op_b, int64_t M, int64_t N, int64_t K, const float* x, int64_t lda, const float* W, int64_t ldb, const float* bias,
+                            float* pre, float* act);
+
+/* dpre = (op(A) op(B)) * gelu'(pre), M x N, pre and dpre dense (leading dimension N): the backward of y = gelu(pre) folded
+ * into the GEMM that produces dy (dX of the linear layer that consumed y; reference: NormalMatMulNode::backward
+ * math_nodes.hpp:475-535 followed by GeLUNode::backward activation_nodes.hpp:157-192 and its BGeLU kernel). */
+GCB_API int gcb_gemm_gelu_bwd_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B, int64_t ldb,
+                          const float* pre, float* dpre);
+
 /* out[(o * batch_inner + i) * rows + r] = sum_c a[o, i, r, c] * b[o, i, r, c]; rows of a and b are addressed through
  * (outer, inner, row) strides in elements, columns are contiguous. */
 GCB_API int gcb_rowdot_batched_f32(gcb_ctx* ctx, float* out, const float* a, int64_t lda, int64_t a_stride_outer, int64_t a_stride_inner,

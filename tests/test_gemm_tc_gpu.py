@@ -212,3 +212,45 @@ def test_softmax_backward_in_the_dp_gemm_epilogue(env, engine, T):
         assert np.all(got[..., blk & ~low] == 0)
     finally:
         ctx.ctx_set_gemm_engine(2)
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (384, 320, 512), (96, 80, 48)])
+@pytest.mark.parametrize("opb", [1, 0])
+def test_gelu_backward_in_the_gemm_epilogue(env, M, N, K, opb):
+    """dpre = (dy W^T) * gelu'(pre) from one call (CTA-pair kernel where the shape allows, two passes otherwise) against float64."""
+    ctx, torch, capi = env
+    dy, pre = rnd(50, M, K) * 1e-2, rnd(51, M, N) * 1.5
+    W = rnd(52, *((N, K) if opb else (K, N)))
+    w = (W.T if opb else W).astype(np.float64)
+    a, b = 0.7978845608, 0.044715
+    x = pre.astype(np.float64)
+    t = np.tanh(a * (x + b * x ** 3))
+    ref = (dy.astype(np.float64) @ w) * (0.5 * (1 + t) + 0.5 * x * (1 - t * t) * a * (1 + 3 * b * x * x))
+    out = torch.full((M, N), float("nan"), device="cuda")
+    ctx.ctx_set_gemm_engine(0)
+    try:
+        ctx.gemm_gelu_bwd_f32(0, opb, M, N, K, torch.from_numpy(dy).cuda(), K, torch.from_numpy(W).cuda(), W.shape[1], torch.from_numpy(pre).cuda(), out)
+        ctx.sync()
+    finally:
+        ctx.ctx_set_gemm_engine(2)
+    assert max_abs_rel(out.cpu().numpy(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (96, 80, 48)])
+def test_linear_gelu_forward_two_outputs(env, M, N, K):
+    """pre = x W + b and act = gelu(pre) from one call; act must be gelu of exactly the pre that was stored."""
+    ctx, torch, capi = env
+    x, W, bias = rnd(60, M, K), rnd(61, K, N) * 0.1, rnd(62, N)
+    pre, act = torch.full((M, N), float("nan"), device="cuda"), torch.full((M, N), float("nan"), device="cuda")
+    ctx.ctx_set_gemm_engine(0)
+    try:
+        ctx.linear_gelu_fwd_f32(0, M, N, K, torch.from_numpy(x).cuda(), K, torch.from_numpy(W).cuda(), N, torch.from_numpy(bias).cuda(), pre, act)
+        ctx.sync()
+    finally:
+        ctx.ctx_set_gemm_engine(2)
+    ref = x.astype(np.float64) @ W.astype(np.float64) + bias
+    assert max_abs_rel(pre.cpu().numpy(), ref) < 1e-5
+    again = torch.empty_like(pre)
+    ctx.gelu_fwd_f32(again, pre, M * N)
+    ctx.sync()
+    assert torch.equal(again, act)
