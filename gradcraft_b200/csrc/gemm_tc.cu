@@ -46,6 +46,7 @@ struct TcParams {
     int64_t work_items;  // tiles to compute (x splits)
     int64_t loop_end;    // bound of the persistent loop: work_items, rounded up to whole rounds where the snake order needs it
     int kept_per_batch;  // causal mode 1: tiles per batch at or below the diagonal
+    int group_batches;   // causal modes 2 / 3: batch items per scheduling group
     int a_chunked, b_chunked;  // MN-major operand described to TMA as (32 floats, k, chunk of 32, batches): one copy fills all 32-float chunks of a tile
     int causal;          // see GemmArgs::causal
     int split_mode;      // 2 (default): one TF32 product of the truncated parts + two BF16 cross products (split_hybrid below);
@@ -303,12 +304,18 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int64_t w, in
         const int64_t G = gridDim.x, round = w / G, c = w - round * G;
         const int64_t q = round * G + ((round & 1) ? G - 1 - c : c);
         t.skip = q >= p.work_items;
-        const int64_t per_class = (int64_t)p.batches * p.tiles_n;
-        const int cls = (int)(q / per_class);
-        const int rem = (int)(q - cls * per_class);
+        // items are ordered by groups of batch items (so that the B operands of the tiles in flight — V, K or Q of a few dozen
+        // heads — stay in L2 while the big A operand streams through), heaviest row tile first inside a group
+        const int64_t per_group = (int64_t)p.group_batches * p.tiles_m * p.tiles_n;
+        const int group = (int)(q / per_group);
+        const int rq = (int)(q - group * per_group);
+        const int gb = min(p.group_batches, p.batches - group * p.group_batches);  // the last group may be smaller
+        const int per_class = max(1, gb * p.tiles_n);
+        const int cls = rq / per_class;
+        const int rem = rq - cls * per_class;
         tile_m = p.causal == 2 ? p.tiles_m - 1 - cls : cls;
         tile_n = rem % p.tiles_n;
-        batch = rem / p.tiles_n;
+        batch = group * p.group_batches + rem / p.tiles_n;
     } else {
         const int per_batch = p.tiles_n * p.tiles_m;
         int r = (int)(w % per_batch); w /= per_batch;
@@ -1192,6 +1199,9 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     static const int pair_tmem_env = [] { const char* e = getenv("GRADC_TC_PAIR_ATMEM"); return e ? atoi(e) : 1; }();
     dim3 grid((unsigned)std::min<int64_t>(p.work_items, (int64_t)kSMs * (BN == 64 ? 2 : 1)), 1, 1);
     p.loop_end = g.causal >= 2 ? (p.work_items + grid.x - 1) / grid.x * grid.x : p.work_items;  // snake order: whole rounds
+    // one group = about one round of the grid: with the snake order a CTA then alternates between a heavy and the matching
+    // light row tile, and a group's B operands (a few MB) are reused while they are still in L2
+    p.group_batches = (int)std::max<int64_t>(1, std::min<int64_t>(batches, (int64_t)grid.x / std::max(1, p.tiles_m * p.tiles_n)));
     int rc;
     if (use_pair) rc = (pair_tmem_env != 0 && p.split_mode == 2) ? launch_pair<true>(ctx, ta, tb, ma, mb, p) : launch_pair<false>(ctx, ta, tb, ma, mb, p);
     else if (BN == 256) rc = launch_bn<256, false>(ctx, ta, tb, ma, mb, p, grid);
