@@ -219,6 +219,31 @@ int gcb_ctx_set_gemm_split_mode(gcb_ctx* ctx, int mode) {
 }
 int gcb_ctx_gemm_split_mode(gcb_ctx* ctx) { return ctx ? ctx->gemm_split_mode : -1; }
 
+// Self-test of the failure path every barrier wait in this library has: one thread waits on an mbarrier that nothing will
+// ever complete, with the same try_wait-with-suspend-hint loop as the GEMM kernels but a caller-given poll budget.  When
+// the budget runs out it records status code 1 / detail 99 and the kernel returns normally: no trap, no hang.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned max_polls) {
+    __shared__ __align__(8) unsigned long long bar;
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(&bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(addr));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (unsigned i = 0; i < max_polls; ++i) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(addr), "r"(0u), "r"(20000u) : "memory");
+        if (ok) return;  // cannot happen: nobody arrives
+    }
+    atomicExch(&status[0], 1);
+    atomicExch(&status[1], 99);
+}
+
+int gcb_selftest_bounded_wait(gcb_ctx* ctx, int max_polls) {
+    GCB_REQUIRE(ctx, "gcb_selftest_bounded_wait: ctx is NULL");
+    GCB_REQUIRE(max_polls >= 1 && max_polls <= 65536, "gcb_selftest_bounded_wait: max_polls must be in [1, 65536] (about 20 us each)");
+    cudaSetDevice(ctx->device);
+    bounded_wait_selftest_kernel<<<1, 1, 0, ctx->stream>>>(ctx->d_status, (unsigned)max_polls);
+    return after_launch(ctx, "bounded_wait_selftest");
+}
+
 int gcb_ctx_sync(gcb_ctx* ctx) {
     GCB_REQUIRE(ctx, "gcb_ctx_sync: ctx is NULL");
     GCB_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));

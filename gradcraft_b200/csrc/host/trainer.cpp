@@ -189,6 +189,18 @@ int gct_load_checkpoint(gct_trainer* tr, const char* model_path, const char* opt
     });
 }
 
+// Token-level generation with the trainer's model (the reference's GPTGenerator::run_inference without its tokenizer).
+int gct_generate(gct_trainer* tr, const int64_t* start_tokens, int64_t n_start, int64_t context_length, int64_t max_tokens, int64_t num_sequences, float temperature, int64_t top_k,
+                 int64_t* out_tokens) {
+    return guarded([&] {
+        if (!tr || !start_tokens || !out_tokens || n_start < 1) throw std::runtime_error("gct_generate: bad arguments");
+        std::vector<int64_t> start(start_tokens, start_tokens + n_start);
+        std::optional<float> temp = temperature > 0.0f ? std::optional<float>(temperature) : std::nullopt;
+        std::vector<int64_t> toks = generate_tokens(tr->forward, start, context_length, max_tokens, num_sequences, tr->gpu, temp, top_k);
+        std::copy(toks.begin(), toks.end(), out_tokens);
+    });
+}
+
 int gct_sync(gct_trainer* tr) {
     return guarded([&] { gcb_check(gcb_ctx_sync(Backend::get().ctx(tr->gpu)), "gct_sync"); });
 }

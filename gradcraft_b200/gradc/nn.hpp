@@ -14,6 +14,7 @@
 #include <thread>
 #include <deque>
 #include <condition_variable>
+#include <algorithm>
 #include <cmath>
 #include <filesystem>
 #include <fstream>
@@ -786,6 +787,61 @@ public:
         return norm;
     }
 };
+
+// ---- generation (nn/generators/gpt_generator.hpp:12-132, token level) ------------------------------------------------------
+// The reference's inference loop without its tokenizer: the whole context is re-forwarded for every new token (no KV cache,
+// as in the reference), the last position's logits decide the next token — argmax when no temperature is given, otherwise
+// softmax(logits / temperature) restricted to the top_k most likely tokens and sampled with the reference's generator
+// (std::mt19937(67), std::nth_element, std::discrete_distribution; gpt_generator.hpp:23-25, 71-95).
+// `forward` maps (B, L) int64 tokens on the device to (B, L, V) logits: any of the GPT modules of this file.
+// Returns num_sequences x max_tokens token ids, every sequence starting with start_tokens.
+template <class Forward>
+std::vector<int64_t> generate_tokens(Forward&& forward, const std::vector<int64_t>& start_tokens, int64_t context_length, int64_t max_tokens, int64_t num_sequences, Device infer_device,
+                                     std::optional<float> temperature = std::nullopt, int64_t top_k = 30) {
+    const int64_t start = (int64_t)start_tokens.size();
+    if (start < 1) throw std::runtime_error("generate_tokens: at least one start token is needed.");
+    if (start >= max_tokens) throw std::runtime_error("Tokenized start_text is >= max_tokens in GPT inference.");
+    if (!infer_device.is_cuda()) throw std::runtime_error("generate_tokens: the inference device must be a CUDA device.");
+    std::mt19937 rng;
+    if (temperature.has_value()) rng = std::mt19937(67);
+    std::vector<int64_t> tokens((size_t)(num_sequences * max_tokens), 0);
+    for (int64_t b = 0; b < num_sequences; ++b) std::copy(start_tokens.begin(), start_tokens.end(), tokens.begin() + b * max_tokens);
+    gcb_ctx* c = Backend::get().ctx(infer_device);
+    std::vector<float> row;
+    for (int64_t step = start; step < max_tokens; ++step) {
+        const int64_t lo = std::max<int64_t>(0, step - context_length), L = step - lo;
+        Tensor<int64_t> ctx_host({num_sequences, L}, Device(DeviceType::CPU), uninitialized);
+        for (int64_t b = 0; b < num_sequences; ++b) std::copy(tokens.begin() + b * max_tokens + lo, tokens.begin() + b * max_tokens + step, ctx_host.data_ptr() + b * L);
+        Tensor<int64_t> ctx_dev = ctx_host.to(infer_device);
+        Tensor<float> logits = forward(ctx_dev);
+        logits.realize();
+        Tensor<float> dense = logits.is_contiguous() ? logits : logits.contiguous();
+        dense.realize();
+        const int64_t V = dense.shape().back();
+        row.resize((size_t)V);
+        for (int64_t b = 0; b < num_sequences; ++b) {
+            gcb_check(gcb_copy_d2h(c, row.data(), dense.data_ptr() + (b * L + (L - 1)) * V, sizeof(float) * (size_t)V), "logits download");
+            int64_t next;
+            if (!temperature.has_value()) {
+                next = (int64_t)(std::max_element(row.begin(), row.end()) - row.begin());  // first maximum, as argmax does
+            } else {
+                float mx = *std::max_element(row.begin(), row.end());
+                double sum = 0.0;
+                for (float& z : row) { z = std::exp((z - mx) / temperature.value()); sum += z; }
+                std::vector<std::pair<float, int64_t>> cand((size_t)V);
+                for (int64_t i = 0; i < V; ++i) cand[(size_t)i] = {(float)(row[(size_t)i] / sum), i};
+                const int64_t k = std::min(top_k, V);
+                std::nth_element(cand.begin(), cand.begin() + k - 1, cand.end(), [](const auto& a, const auto& b2) { return a.first > b2.first; });
+                std::vector<float> weights((size_t)k);
+                for (int64_t i = 0; i < k; ++i) weights[(size_t)i] = cand[(size_t)i].first;
+                std::discrete_distribution<int64_t> dist(weights.begin(), weights.end());
+                next = cand[(size_t)dist(rng)].second;
+            }
+            tokens[(size_t)(b * max_tokens + step)] = next;
+        }
+    }
+    return tokens;
+}
 
 // ---- data loader (nn/utils/data_loader.hpp:13-92) ------------------------------------------------------------------------
 // Same file format (little-endian uint32 tokens), same shuffled fixed-length windows and the same order of batches as the

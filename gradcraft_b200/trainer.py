@@ -32,6 +32,7 @@ def _lib():
         L.gct_forward_backward.argtypes = [vp, vp, vp, ci, i64, i64, i64, ctypes.POINTER(f32)]
         L.gct_optimizer_step.argtypes = [vp, ctypes.POINTER(f32)]
         L.gct_sync.argtypes = [vp]
+        L.gct_generate.argtypes = [vp, vp, i64, i64, i64, i64, f32, i64, vp]
         L.gct_save_checkpoint.argtypes = [vp, ctypes.c_char_p, ctypes.c_char_p]
         L.gct_load_checkpoint.argtypes = [vp, ctypes.c_char_p, ctypes.c_char_p]
         L.gct_stream.argtypes, L.gct_stream.restype = [vp], vp
@@ -117,6 +118,15 @@ class Trainer:
             tot += l if want_loss else 0.0
         self.optimizer_step()
         return tot
+
+    def generate(self, start_tokens, max_tokens, num_sequences=1, context_length=None, temperature=0.0, top_k=30):
+        """[num_sequences, max_tokens] int64 token ids; argmax decoding unless temperature > 0."""
+        import numpy as np
+
+        start = np.ascontiguousarray(np.asarray(start_tokens, dtype=np.int64))
+        out = np.zeros((num_sequences, max_tokens), dtype=np.int64)
+        self._ok(self.L.gct_generate(self.h, _ptr(start), len(start), context_length or self.shape["T"], max_tokens, num_sequences, temperature, top_k, _ptr(out)))
+        return out
 
     def save_checkpoint(self, model_path, optim_path):
         """Weights and AdamW state in the reference's checkpoint file format."""

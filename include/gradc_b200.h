@@ -60,6 +60,11 @@ GCB_API int gcb_ctx_destroy(gcb_ctx* ctx);
 GCB_API void* gcb_ctx_stream(gcb_ctx* ctx);
 GCB_API int gcb_ctx_device(gcb_ctx* ctx);
 GCB_API int gcb_ctx_sync(gcb_ctx* ctx); /* cudaStreamSynchronize + sticky-error check */
+/* Failure-path self-test (no counterpart in the reference, whose kernels never wait on one another): launches a
+ * one-thread kernel that waits on a barrier nothing completes, gives up after max_polls polls of about 20 us each and
+ * records that in the context's status word, exactly as every bounded wait of the GEMM and norm kernels does.  The next
+ * gcb_ctx_sync returns GCB_TIMEOUT and clears the word; the context stays usable. */
+GCB_API int gcb_selftest_bounded_wait(gcb_ctx* ctx, int max_polls);
 /* Number of kernels this library launched through ctx since creation. */
 GCB_API int64_t gcb_ctx_launch_count(gcb_ctx* ctx);
 /* Which GEMM engine ran last: 0 none, 1 SIMT fp32, 2 tcgen05 (split fp32). */

@@ -39,6 +39,11 @@ GCT_API int gct_optimizer_step(gct_trainer* tr, float* norm_out);
  * (nn/utils/checkpoint.hpp:12-77; train.cpp:174-179 and :100-118).  Arena-resident state moves as one copy per array. */
 GCT_API int gct_save_checkpoint(gct_trainer* tr, const char* model_path, const char* optim_path);
 GCT_API int gct_load_checkpoint(gct_trainer* tr, const char* model_path, const char* optim_path);
+/* Token-level generation (nn/generators/gpt_generator.hpp:12-132 without the tokenizer): num_sequences rows of max_tokens ids
+ * into out_tokens, each starting with the n_start given tokens; the context (at most context_length tokens) is re-forwarded
+ * for every new token.  temperature <= 0: argmax; otherwise top_k sampling with the reference's generator and seed. */
+GCT_API int gct_generate(gct_trainer* tr, const int64_t* start_tokens, int64_t n_start, int64_t context_length, int64_t max_tokens, int64_t num_sequences, float temperature,
+                         int64_t top_k, int64_t* out_tokens);
 GCT_API int gct_sync(gct_trainer* tr);
 GCT_API void* gct_stream(gct_trainer* tr);           /* cudaStream_t the step runs on */
 GCT_API void* gct_context(gct_trainer* tr);          /* gcb_ctx* of include/gradc_b200.h */

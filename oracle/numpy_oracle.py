@@ -252,6 +252,29 @@ class GPTOracle:
         g[pre + ".gamma"] = dg
         return dx
 
+    def logits(self, w, X):
+        """Forward only: (B, T, V) logits of the tied head (the forward half of loss_and_grads; nn/layers/gpt.hpp:99-110)."""
+        B, T = X.shape
+        C, H = self.C, self.H
+        D = C // H
+        x = (w["token_embed.embeds"][X] + w["pos_embed.pos_embeds"][:T][None]).astype(F32)
+        split = lambda t: t.reshape(B, T, H, D).transpose(0, 2, 1, 3)
+        for i in range(self.L):
+            b = "block_%d." % i
+            h1, _ = self._norm_f(w, b + "norm1", x)
+            q, k, v = (linear_fwd(h1, w[b + "attn.%s_proj.W" % n], w[b + "attn.%s_proj.b" % n]) for n in "qkv")
+            o, _ = attention_fwd(split(q), split(k), split(v))
+            x = x + linear_fwd(o.transpose(0, 2, 1, 3).reshape(B, T, C), w[b + "attn.out_proj.W"], w[b + "attn.out_proj.b"])
+            h2, _ = self._norm_f(w, b + "norm2", x)
+            if self.arch == "lngelu":
+                x = x + linear_fwd(gelu_fwd(linear_fwd(h2, w[b + "mlp.fc1.W"], w[b + "mlp.fc1.b"])), w[b + "mlp.fc2.W"], w[b + "mlp.fc2.b"])
+            else:
+                u1 = linear_fwd(h2, w[b + "mlp.w1.W"], w[b + "mlp.w1.b"])
+                u2 = linear_fwd(h2, w[b + "mlp.w2.W"], w[b + "mlp.w2.b"])
+                x = x + linear_fwd(swiglu_fwd(u1, u2), w[b + "mlp.w3.W"], w[b + "mlp.w3.b"])
+        xf, _ = self._norm_f(w, "final_norm", x)
+        return (xf.reshape(B * T, C) @ w["token_embed.embeds"].T).astype(F32).reshape(B, T, -1)
+
     def loss_and_grads(self, w, X, Y, upstream=1.0):
         B, T = X.shape
         C, H = self.C, self.H

@@ -508,3 +508,17 @@ def test_causal_softmax_band_variants(env, T, band):
     rd = O.causal_softmax_bwd(dp, rp[None], 0.125)[0]
     assert max_abs_rel(np.where(inside, d, 0), np.where(inside, rd, 0)) < TOL
     assert np.all(d[:, ~inside] == 5.0)
+
+
+def test_bounded_wait_that_runs_out_is_reported_and_the_context_survives(env):
+    """The failure path of every barrier wait: a wait that nothing completes gives up after its poll budget (~10 ms here),
+    the kernel returns normally, sync reports GCB_TIMEOUT once, and the same context keeps computing."""
+    ctx, torch, capi = env
+    ctx.selftest_bounded_wait(512)
+    with pytest.raises(capi.GcbError) as e:
+        ctx.sync()
+    assert e.value.status == capi.TIMEOUT
+    x = torch.empty(1000, device="cuda")
+    ctx.fill_f32(x, 2.5, 1000)
+    ctx.sync()  # the status word was cleared
+    assert float(x.sum()) == 2500.0
