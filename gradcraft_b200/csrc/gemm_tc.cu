@@ -246,7 +246,10 @@ struct RoleTrace {
 #define TR_BEGIN(s) RoleTrace tr(s)
 #define TR_WAIT(call) [&] { const long long tr_a = tr_clock(); const bool tr_r = (call); tr.wait += tr_clock() - tr_a; return tr_r; }()
 #define TR_END() tr.done()
+// second counter of the issuer: cycles waiting for the epilogue to hand an accumulator back (slot 3, summed into g_tc_trace[6])
+#define TR_WAIT2(call) [&] { const long long tr_a = tr_clock(); const bool tr_r = (call); atomicAdd(&g_tc_trace[6], (unsigned long long)(tr_clock() - tr_a)); return tr_r; }()
 #else
+#define TR_WAIT2(call) (call)
 #define TR_BEGIN(s)
 #define TR_WAIT(call) (call)
 #define TR_END()
@@ -805,7 +808,7 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                 const TileCoord tc = pair_tile_coord(p, w);
                 if (tc.skip) continue;
                 const uint32_t buf = lt % NACC;
-                ok = mbar_wait(acc_empty_bar(buf), ((lt / NACC) & 1u) ^ 1u, p.status, 15);
+                ok = TR_WAIT2(mbar_wait(acc_empty_bar(buf), ((lt / NACC) & 1u) ^ 1u, p.status, 15));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + buf * BN;
