@@ -254,3 +254,37 @@ def test_linear_gelu_forward_two_outputs(env, M, N, K):
     ctx.gelu_fwd_f32(again, pre, M * N)
     ctx.sync()
     assert torch.equal(again, act)
+
+
+def test_pair_kernel_batched_and_causal_paths(env):
+    """Head dimension 256 sends every attention GEMM to the CTA-pair kernel (N = 256 or K >= 256): batched operands with
+    two-level strides and all three causal variants there, against float64."""
+    ctx, torch, capi = env
+    Bn, H, T, D = 2, 2, 512, 256
+    C = H * D
+    q, k, v = rnd(70, Bn, T, C), rnd(71, Bn, T, C), rnd(72, Bn, T, C)
+    Q, Kd, Vd = (torch.from_numpy(x).cuda() for x in (q, k, v))
+    heads = lambda a: a.reshape(Bn, T, H, D).transpose(0, 2, 1, 3).astype(np.float64)
+    untok = lambda a: a.transpose(0, 2, 1, 3).reshape(Bn, T, C)
+    low = np.tril(np.ones((T, T), bool))
+    S = torch.full((Bn * H, T, T), float("nan"), device="cuda")
+    ctx.gemm_batched_causal_f32(0, 1, T, T, D, 1.0, Q, C, T * C, D, Kd, C, T * C, D, 0.0, S, T, H * T * T, T * T, Bn, H, 1)
+    ctx.sync()
+    assert ctx.ctx_last_gemm_engine() == 2
+    ref = heads(q) @ heads(k).transpose(0, 1, 3, 2)
+    s = S.cpu().numpy().reshape(Bn, H, T, T)
+    assert float(np.abs(s[..., low] - ref[..., low]).max() / np.abs(ref).max()) < TOL
+    Sf = torch.empty(Bn * H, T, T, device="cuda")
+    ctx.gemm_batched_f32(0, 1, T, T, D, 1.0, Q, C, T * C, D, Kd, C, T * C, D, 0.0, Sf, T, H * T * T, T * T, Bn, H)
+    ctx.sync()
+    assert max_abs_rel(Sf.cpu().numpy().reshape(Bn, H, T, T), ref) < TOL
+    p = np.tril(np.abs(ref) / np.abs(ref).sum(-1, keepdims=True))  # any lower-triangular matrix will do
+    P = torch.from_numpy(p.reshape(Bn * H, T, T).astype(np.float32)).cuda()
+    p = P.cpu().numpy().reshape(Bn, H, T, T).astype(np.float64)
+    O = torch.zeros(Bn, T, C, device="cuda")
+    ctx.gemm_batched_causal_f32(0, 0, T, D, T, 1.0, P, T, H * T * T, T * T, Vd, C, T * C, D, 0.0, O, C, T * C, D, Bn, H, 2)
+    dV = torch.zeros(Bn, T, C, device="cuda")
+    ctx.gemm_batched_causal_f32(1, 0, T, D, T, 1.0, P, T, H * T * T, T * T, Q, C, T * C, D, 0.0, dV, C, T * C, D, Bn, H, 3)
+    ctx.sync()
+    assert max_abs_rel(O.cpu().numpy(), untok(p @ heads(v))) < TOL
+    assert max_abs_rel(dV.cpu().numpy(), untok(p.transpose(0, 1, 3, 2) @ heads(q))) < TOL
