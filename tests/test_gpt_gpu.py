@@ -11,7 +11,8 @@ from tests.helpers import assert_grads_close, load_golden, split_prefix
 pytestmark = pytest.mark.gpu
 
 
-def run_case(name, engine=None):
+def run_case(name, engine=None, split_mode=None):
+    from gradcraft_b200 import capi
     from gradcraft_b200.trainer import Trainer
 
     arch, V, T, C, H, L, F, B, steps, accum, clip, perturb = GPT_CASES[name]
@@ -21,6 +22,8 @@ def run_case(name, engine=None):
     tr = Trainer(arch, V, T, C, H, L, F, lr=HYPER["lr"], beta1=HYPER["beta1"], beta2=HYPER["beta2"], wd=HYPER["wd"], eps=HYPER["eps"], norm_eps=HYPER["norm_eps"], clip=clip)
     try:
         assert tr.num_params() == sum(v.size for v in w.values())
+        if split_mode is not None:
+            capi.lib().ctx_set_gemm_split_mode(tr.context(), split_mode)
         tr.load(w)
         losses = []
         for step in range(1, steps + 1):
@@ -52,6 +55,11 @@ def run_case(name, engine=None):
 @pytest.mark.parametrize("name", ["mini_lngelu", "mini_rmsswiglu", "config1_lngelu"])
 def test_training_matches_reference(name):
     run_case(name)
+
+
+def test_training_matches_reference_with_three_tf32_products():
+    """The same parity bar with the GEMM engine in split mode 1 (classic 3xTF32) instead of the default TF32 + 2 x BF16."""
+    run_case("config1_lngelu", split_mode=1)
 
 
 def test_arena_order_follows_gradient_finality():
