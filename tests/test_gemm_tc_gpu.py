@@ -288,3 +288,26 @@ def test_pair_kernel_batched_and_causal_paths(env):
     ctx.sync()
     assert max_abs_rel(O.cpu().numpy(), untok(p @ heads(v))) < TOL
     assert max_abs_rel(dV.cpu().numpy(), untok(p.transpose(0, 1, 3, 2) @ heads(q))) < TOL
+
+
+def test_fused_entry_points_accept_empty_problems_and_reject_bad_arguments(env):
+    """Zero-sized calls are no-ops; aliasing and missing operands are refused with GCB_INVALID_ARG before any launch."""
+    ctx, torch, capi = env
+    z = torch.zeros(16, device="cuda")
+    ctx.rowdot_batched_f32(z, z, 4, 0, 0, z, 4, 0, 0, 0, 4, 1, 1)           # no rows
+    ctx.rowdot_batched_f32(z, z, 4, 0, 0, z, 4, 0, 0, 4, 4, 0, 3)           # no batch items
+    ctx.gemm_batched_softmax_bwd_f32(0, 1, 0, 8, 1.0, z, 8, 0, 0, z, 8, 0, 0, z, 4, 0, 0, 1, 1, z[4:], z, 1.0)  # M = 0
+    ctx.gemm_gelu_bwd_f32(0, 0, 0, 4, 4, z, 4, z, 4, z, z[4:])              # M = 0 (pre / dpre only have to differ)
+    ctx.sync()
+    with pytest.raises(capi.GcbError) as e:
+        ctx.gemm_gelu_bwd_f32(0, 0, 4, 4, 4, z, 4, z, 4, z, z)              # dpre aliases pre
+    assert e.value.status == capi.INVALID_ARG
+    with pytest.raises(capi.GcbError) as e:
+        ctx.linear_gelu_fwd_f32(0, 4, 4, 4, z, 4, z, 4, None, z, z)         # act aliases pre
+    assert e.value.status == capi.INVALID_ARG
+    with pytest.raises(capi.GcbError) as e:
+        ctx.gemm_batched_softmax_bwd_f32(0, 1, 4, 4, 1.0, z, 4, 0, 0, z, 4, 0, 0, z, 4, 0, 0, 1, 1, None, z, 1.0)  # no probabilities
+    assert e.value.status == capi.INVALID_ARG
+    with pytest.raises(capi.GcbError) as e:
+        ctx.ctx_set_gemm_split_mode(7)
+    assert e.value.status == capi.INVALID_ARG
