@@ -76,14 +76,26 @@ def build_trainer(verbose=False, force=False):
 TRAIN_BIN = os.path.join(OBJ, "train_ref")
 
 
-def build_reference_train(reference_root="/root/reference", verbose=False):
+def reference_root():
+    """Where the reference project's source tree is: the GRADC_REFERENCE_ROOT environment variable, else a directory named
+    `reference` beside this repository.  Returns None when neither holds a GradCraft tree (prebuilt checker binaries are then used as they are)."""
+    cands = [os.environ.get("GRADC_REFERENCE_ROOT"), os.path.join(HERE, "..", "..", "reference")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "gradc")):
+            return os.path.abspath(c)
+    return None
+
+
+def build_reference_train(reference_root=None, verbose=False):
     """Compiles the reference's own train.cpp, unchanged, against gradcraft_b200/gradc and links it with the sm_100a backend.
     The source is read where it lies (a scratch copy is needed only because a quoted include searches the including file's
     directory first); nothing of it is stored in this repository.  Returns the binary's path, or None without the reference."""
     import shutil
     import tempfile
 
-    src = os.path.join(reference_root, "train.cpp")
+    if reference_root is None:
+        reference_root = globals()["reference_root"]()
+    src = os.path.join(reference_root or "", "train.cpp")
     if not os.path.exists(src):
         return TRAIN_BIN if os.path.exists(TRAIN_BIN) else None
     hdrs = tuple(os.path.join(HERE, "gradc", f) for f in os.listdir(os.path.join(HERE, "gradc")))

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <string>
@@ -15,6 +16,7 @@
 namespace gcb {
 
 constexpr int kSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized as multiples of this
+constexpr int kMaxDevices = 64;  // per-device caches (function attributes, symbol addresses) are indexed by the context's device
 
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
@@ -62,6 +64,7 @@ struct gcb_ctx {
     cudaEvent_t ev_compute = nullptr, ev_comm = nullptr;
     gcb::Arena arena;
     int64_t launches = 0;
+    std::vector<std::pair<const char*, int64_t>> launches_by_name;  // per kernel family (the name each call site passes to after_launch)
     int gemm_engine = 0;       // 0 auto, 1 simt, 2 tcgen05
     int last_gemm_engine = 0;
     int gemm_split_mode = 2;   // see gcb_ctx_set_gemm_split_mode
@@ -90,6 +93,14 @@ struct Scratch {  // RAII arena block used inside one entry point
 
 inline int after_launch(gcb_ctx* ctx, const char* what, int n = 1) {
     ctx->launches += n;
+    {   // tally per kernel family: a few dozen string literals, found by address first
+        auto& v = ctx->launches_by_name;
+        size_t i = 0;
+        for (; i < v.size(); ++i) if (v[i].first == what) break;
+        if (i == v.size()) for (i = 0; i < v.size(); ++i) if (std::strcmp(v[i].first, what) == 0) break;
+        if (i == v.size()) v.emplace_back(what, 0);
+        v[i].second += n;
+    }
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) return cuda_fail(cudaGetLastError(), what);
     return GCB_OK;

@@ -155,7 +155,7 @@ static int ctx_create_common(int device, void* stream, bool own, gcb_ctx** out) 
         set_error("gcb_ctx_create: no CUDA device is visible (%s); this backend has no CPU fallback", e == cudaSuccess ? "device count 0" : cudaGetErrorString(e));
         return GCB_CUDA_ERROR;
     }
-    GCB_REQUIRE(device >= 0 && device < count, "gcb_ctx_create: device %d out of range (%d visible)", device, count);
+    GCB_REQUIRE(device >= 0 && device < count && device < kMaxDevices, "gcb_ctx_create: device %d out of range (%d visible)", device, count);
     GCB_CHECK_CUDA(cudaSetDevice(device));
     cudaDeviceProp prop;
     GCB_CHECK_CUDA(cudaGetDeviceProperties(&prop, device));
@@ -205,6 +205,13 @@ int gcb_ctx_destroy(gcb_ctx* ctx) {
 void* gcb_ctx_stream(gcb_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 int gcb_ctx_device(gcb_ctx* ctx) { return ctx ? ctx->device : -1; }
 int64_t gcb_ctx_launch_count(gcb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+int64_t gcb_ctx_launch_count_named(gcb_ctx* ctx, const char* prefix) {
+    if (!ctx || !prefix) return 0;
+    const size_t n = strlen(prefix);
+    int64_t total = 0;
+    for (const auto& kv : ctx->launches_by_name) if (strncmp(kv.first, prefix, n) == 0) total += kv.second;
+    return total;
+}
 int gcb_ctx_last_gemm_engine(gcb_ctx* ctx) { return ctx ? ctx->last_gemm_engine : 0; }
 int gcb_ctx_set_gemm_engine(gcb_ctx* ctx, int engine) {
     GCB_REQUIRE(ctx && engine >= 0 && engine <= 2, "gcb_ctx_set_gemm_engine: engine must be 0, 1 or 2");
@@ -244,9 +251,9 @@ int gcb_selftest_bounded_wait(gcb_ctx* ctx, int max_polls) {
     return after_launch(ctx, "bounded_wait_selftest");
 }
 
-int gcb_ctx_sync(gcb_ctx* ctx) {
-    GCB_REQUIRE(ctx, "gcb_ctx_sync: ctx is NULL");
-    GCB_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+// Reads the device status word after the stream has been synchronised: a kernel that gave up on a bounded wait, or an
+// index / target that was skipped because it lay outside its table, turns into an error of the call that blocked.
+static int check_status_word(gcb_ctx* ctx) {
     int st[4];
     GCB_CHECK_CUDA(cudaMemcpy(st, ctx->d_status, sizeof(st), cudaMemcpyDeviceToHost));
     if (st[0] != 0) {
@@ -259,6 +266,12 @@ int gcb_ctx_sync(gcb_ctx* ctx) {
         return GCB_TIMEOUT;
     }
     return GCB_OK;
+}
+
+int gcb_ctx_sync(gcb_ctx* ctx) {
+    GCB_REQUIRE(ctx, "gcb_ctx_sync: ctx is NULL");
+    GCB_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return check_status_word(ctx);
 }
 
 int gcb_arena_alloc(gcb_ctx* ctx, size_t bytes, void** out) {
@@ -297,7 +310,9 @@ int gcb_copy_d2h(gcb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     GCB_REQUIRE(ctx && (bytes == 0 || (dst && src)), "gcb_copy_d2h: NULL argument");
     GCB_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     GCB_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
-    return GCB_OK;
+    // the host blocks here anyway (Tensor::item() of the loss, gradient and checkpoint reads): the one place per training step
+    // where a failed launch can be reported before its results are used
+    return check_status_word(ctx);
 }
 int gcb_copy_h2d_async(gcb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     GCB_REQUIRE(ctx && (bytes == 0 || (dst && src)), "gcb_copy_h2d_async: NULL argument");

@@ -5,24 +5,8 @@
 
 using namespace gcb;
 
-static int run_gemm(gcb_ctx* ctx, int op_a, int op_b, const GemmArgs& g, const char* who) {
-    GCB_REQUIRE((op_a == GCB_OP_N || op_a == GCB_OP_T) && (op_b == GCB_OP_N || op_b == GCB_OP_T), "%s: op must be GCB_OP_N or GCB_OP_T", who);
-    GCB_REQUIRE(g.M >= 0 && g.N >= 0 && g.K >= 0, "%s: negative dimension", who);
-    if (g.M == 0 || g.N == 0 || g.batch_outer * g.batch_inner == 0) return GCB_OK;
-    GCB_REQUIRE(g.C && (g.K == 0 || (g.A && g.B)), "%s: NULL operand", who);
-    const bool ta = op_a == GCB_OP_T, tb = op_b == GCB_OP_T;
-    GCB_REQUIRE(g.lda >= (ta ? g.M : g.K) && g.ldb >= (tb ? g.K : g.N) && g.ldc >= g.N, "%s: leading dimension smaller than the row length (lda %lld ldb %lld ldc %lld)", who,
-                (long long)g.lda, (long long)g.ldb, (long long)g.ldc);
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
-    if (ctx->prof_on) {
-        if (ctx->prof_used + 2 > ctx->prof_events.size()) {
-            for (int i = 0; i < 512; ++i) { cudaEvent_t e; GCB_CHECK_CUDA(cudaEventCreate(&e)); ctx->prof_events.push_back(e); }
-        }
-        e0 = ctx->prof_events[ctx->prof_used++];
-        e1 = ctx->prof_events[ctx->prof_used++];
-        ctx->prof_flops += 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)(g.batch_outer * g.batch_inner);
-        GCB_CHECK_CUDA(cudaEventRecord(e0, ctx->stream));
-    }
+// Engine choice for one validated problem; no timing here, so the GELU fallback below may call it again freely.
+static int dispatch_gemm(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g, const char* who) {
     int rc = GCB_UNSUPPORTED;
     if (ctx->gemm_engine != 1 && gemm_tc_eligible(ta, tb, g)) rc = gemm_tc_launch(ctx, ta, tb, g);
     if (rc == GCB_UNSUPPORTED && (g.gelu_pre || g.gelu_act)) {
@@ -30,10 +14,9 @@ static int run_gemm(gcb_ctx* ctx, int op_a, int op_b, const GemmArgs& g, const c
         GemmArgs plain = g;
         plain.gelu_pre = nullptr;
         plain.gelu_act = nullptr;
-        rc = run_gemm(ctx, op_a, op_b, plain, who);
+        rc = dispatch_gemm(ctx, ta, tb, plain, who);
         if (rc == GCB_OK && g.gelu_pre) rc = gcb_gelu_bwd_f32(ctx, g.C, g.C, g.gelu_pre, g.M * g.N, 0);
         if (rc == GCB_OK && g.gelu_act) rc = gcb_gelu_fwd_f32(ctx, g.gelu_act, g.C, g.M * g.N);
-        if (e1) GCB_CHECK_CUDA(cudaEventRecord(e1, ctx->stream));
         return rc;
     }
     if (rc == GCB_UNSUPPORTED) {
@@ -44,7 +27,32 @@ static int run_gemm(gcb_ctx* ctx, int op_a, int op_b, const GemmArgs& g, const c
         rc = gemm_simt_launch(ctx, ta, tb, g);
         if (rc == GCB_OK && g.sm_probs) rc = softmax_bwd_apply_launch(ctx, g);  // this engine has no fused epilogue: same arithmetic as a second pass
     }
-    if (e1) GCB_CHECK_CUDA(cudaEventRecord(e1, ctx->stream));
+    return rc;
+}
+
+// Validation, then the dispatch bracketed by one pair of timing events when profiling is on: a product is counted once
+// whatever path it takes, and the closing event is recorded on every exit so that gcb_profile_gemm_end never meets an
+// unrecorded event.
+static int run_gemm(gcb_ctx* ctx, int op_a, int op_b, const GemmArgs& g, const char* who) {
+    GCB_REQUIRE((op_a == GCB_OP_N || op_a == GCB_OP_T) && (op_b == GCB_OP_N || op_b == GCB_OP_T), "%s: op must be GCB_OP_N or GCB_OP_T", who);
+    GCB_REQUIRE(g.M >= 0 && g.N >= 0 && g.K >= 0, "%s: negative dimension", who);
+    if (g.M == 0 || g.N == 0 || g.batch_outer * g.batch_inner == 0) return GCB_OK;
+    GCB_REQUIRE(g.C && (g.K == 0 || (g.A && g.B)), "%s: NULL operand", who);
+    const bool ta = op_a == GCB_OP_T, tb = op_b == GCB_OP_T;
+    GCB_REQUIRE(g.lda >= (ta ? g.M : g.K) && g.ldb >= (tb ? g.K : g.N) && g.ldc >= g.N, "%s: leading dimension smaller than the row length (lda %lld ldb %lld ldc %lld)", who,
+                (long long)g.lda, (long long)g.ldb, (long long)g.ldc);
+    if (!ctx->prof_on) return dispatch_gemm(ctx, ta, tb, g, who);
+    if (ctx->prof_used + 2 > ctx->prof_events.size()) {
+        for (int i = 0; i < 512; ++i) { cudaEvent_t e; GCB_CHECK_CUDA(cudaEventCreate(&e)); ctx->prof_events.push_back(e); }
+    }
+    cudaEvent_t e0 = ctx->prof_events[ctx->prof_used], e1 = ctx->prof_events[ctx->prof_used + 1];
+    GCB_CHECK_CUDA(cudaEventRecord(e0, ctx->stream));
+    const int rc = dispatch_gemm(ctx, ta, tb, g, who);
+    GCB_CHECK_CUDA(cudaEventRecord(e1, ctx->stream));
+    if (rc == GCB_OK) {  // a refused problem leaves no trace in the tally
+        ctx->prof_used += 2;
+        ctx->prof_flops += 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)(g.batch_outer * g.batch_inner);
+    }
     return rc;
 }
 

@@ -536,7 +536,9 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
         const int c_begin = (ew >> 2) * COLS_PER_WARP, c_end = c_begin + COLS_PER_WARP;
         float* stg = reinterpret_cast<float*>(gen_base + TC_STAGES * S::STAGE_BYTES) + ew * 32 * S::EPI_PITCH;
         const bool to_partial = p.splits > 1;
-        const bool vec_ok = to_partial ? (p.N % 4 == 0) : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
+        // the float4 fast path needs every array the epilogue touches with vector accesses on 16-byte boundaries: C and, laid out like C, the probabilities
+        const bool vec_ok = to_partial ? (p.N % 4 == 0)
+                                       : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.sm_probs) | (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
         const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
         const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;  // store phase: 4 rows x 8 float4 per instruction (128 B per row)
         uint32_t lt = 0;
@@ -909,7 +911,10 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
         const int c_begin = (ew >> 2) * COLS_PER_WARP, c_end = c_begin + COLS_PER_WARP;
         float* stg = reinterpret_cast<float*>(gen_base + NST * S::STAGE_BYTES) + ew * 32 * S::EPI_PITCH;
         const bool to_partial = p.splits > 1;
-        const bool vec_ok = to_partial ? (p.N % 4 == 0) : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
+        // the float4 fast path needs C and the GELU side arrays (laid out like C) on 16-byte boundaries; otherwise the scalar path runs
+        const bool vec_ok = to_partial ? (p.N % 4 == 0)
+                                       : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.gelu_pre) | reinterpret_cast<uintptr_t>(p.gelu_act) |
+                                                              (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
         const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
         const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;
         uint32_t lt = 0;
@@ -1088,8 +1093,8 @@ static int launch_bn(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, cons
 #define GCB_TC(AM, BMN)                                                                                                   \
     do {                                                                                                                  \
         auto kfn = gemm_tc_kernel<BN, AM, BMN, A_TM>;                                                                     \
-        static bool attr_done = false;                                                                                    \
-        if (!attr_done) { GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_done = true; } \
+        static bool attr_done[kMaxDevices] = {}; /* function attributes belong to a device, not to the process */       \
+        if (!attr_done[ctx->device]) { GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_done[ctx->device] = true; } \
         kfn<<<grid, TcSmem<BN, A_TM>::THREADS, smem, ctx->stream>>>(ma, mb, p);                                                          \
     } while (0)
     // A "transposed" (stored K x M) is MN-major; B "normal" (stored K x N) is MN-major
@@ -1120,16 +1125,16 @@ static int launch_pair(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, co
 #define GCB_PAIR(AM, BMN)                                                                                                   \
     do {                                                                                                                    \
         auto kfn = gemm_tc_pair_kernel<AM, BMN, A_TM>;                                                                            \
-        static bool attr_done = false;                                                                                      \
-        static int max_clusters = 0;                                                                                        \
-        if (!attr_done) {                                                                                                   \
+        static int max_clusters[kMaxDevices] = {}; /* per device; 0 = not yet queried */                                    \
+        if (max_clusters[ctx->device] == 0) {                                                                               \
             GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));              \
             cfg.gridDim = dim3(kSMs, 1, 1);                                                                                 \
-            GCB_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&max_clusters, kfn, &cfg)); /* pairs that can be co-resident */   \
-            if (max_clusters < 1) { set_error("gemm (pair): no cluster of two CTAs fits on this device"); return GCB_UNSUPPORTED; } \
-            attr_done = true;                                                                                               \
+            int mc = 0;                                                                                                     \
+            GCB_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&mc, kfn, &cfg)); /* pairs that can be co-resident */             \
+            if (mc < 1) { set_error("gemm (pair): no cluster of two CTAs fits on this device"); return GCB_UNSUPPORTED; }   \
+            max_clusters[ctx->device] = mc;                                                                                 \
         }                                                                                                                   \
-        cfg.gridDim = dim3((unsigned)(2 * std::min<int64_t>(p.work_items, max_clusters)), 1, 1);                            \
+        cfg.gridDim = dim3((unsigned)(2 * std::min<int64_t>(p.work_items, max_clusters[ctx->device])), 1, 1);               \
         GCB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kfn, ma, mb, p));                                                           \
     } while (0)
     if (ta && !tb) GCB_PAIR(true, true);
@@ -1211,7 +1216,9 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     else if (BN == 128) rc = a_tmem ? launch_bn<128, true>(ctx, ta, tb, ma, mb, p, grid) : launch_bn<128, false>(ctx, ta, tb, ma, mb, p, grid);
     else rc = a_tmem ? launch_bn<64, true>(ctx, ta, tb, ma, mb, p, grid) : launch_bn<64, false>(ctx, ta, tb, ma, mb, p, grid);
     if (rc) return rc;
-    rc = after_launch(ctx, "gemm_tc");
+    const char* family = use_pair ? (g.gelu_act ? "gemm_tc_pair_gelu_fwd" : g.gelu_pre ? "gemm_tc_pair_gelu_bwd" : "gemm_tc_pair")
+                         : BN == 256 ? (g.sm_probs ? "gemm_tc_256_softmax_bwd" : "gemm_tc_256") : BN == 128 ? "gemm_tc_128" : "gemm_tc_64";
+    rc = after_launch(ctx, family);
     if (rc) return rc;
     if (splits > 1) {
         const int64_t total = g.M * g.N;

@@ -8,6 +8,8 @@
 // column sums in registers across all the rows it visits; the per-warp sums are combined through shared memory
 // into one partial per CTA and a second tiny kernel adds the CTA partials in a fixed order (no atomics, so the
 // result is deterministic).  Other shapes take a CTA-per-row kernel with the same arithmetic.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace gcb {
@@ -446,6 +448,7 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
     const bool fast = cols % 4 == 0 && cols <= 1024 && aligned16(x) && aligned16(dy) && aligned16(gamma) && (dx == nullptr || aligned16(dx));
     const char* name = IS_LN ? "layernorm_bwd" : "rmsnorm_bwd";
     if (fast && rows >= 4 * kSMs * kRingWarps && (dx == nullptr || aligned16(dx))) {
+        name = IS_LN ? "layernorm_bwd_ring" : "rmsnorm_bwd_ring";
         // large inputs: one persistent CTA per SM, rows staged through shared memory by bulk async copies
         const int64_t blocks = kSMs;
         Scratch sc(ctx);
@@ -455,8 +458,8 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
 #define GCB_RING(N)                                                                                                                                      \
         do {                                                                                                                                             \
             auto kfn = norm_bwd_ring<N, IS_LN>;                                                                                                          \
-            static bool attr_done = false;                                                                                                               \
-            if (!attr_done) { GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_done = true; }     \
+            static bool attr_done[kMaxDevices] = {}; /* function attributes belong to a device */                                                        \
+            if (!attr_done[ctx->device]) { GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_done[ctx->device] = true; } \
             kfn<<<(unsigned)blocks, kRingWarps * 32, smem, ctx->stream>>>(dx, sc.as<float>(), dy, x, gamma, s0, s1, rows, (int)cols, acc_dx, want_params ? 1 : 0, ctx->d_status); \
         } while (0)
         if (n == 1) GCB_RING(1); else if (n == 2) GCB_RING(2); else if (n == 4) GCB_RING(4); else if (n == 6) GCB_RING(6); else GCB_RING(8);
@@ -470,6 +473,7 @@ static int norm_bwd(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const 
         return rc;
     }
     if (fast) {
+        name = IS_LN ? "layernorm_bwd_warp" : "rmsnorm_bwd_warp";
         // 3 CTAs of 4 warps per SM: ~170 registers per thread, 96 KB of row data in flight per SM
         int64_t blocks = std::min<int64_t>((rows + kNormWarps - 1) / kNormWarps, (int64_t)kSMs * 3);
         Scratch sc(ctx);
@@ -522,19 +526,24 @@ constexpr size_t kNoAllocFloats = (size_t)kNoAllocMaxBlocks * 2 * kNoAllocMaxCol
 static __device__ __align__(256) float g_ln_bwd_partials[kNoAllocFloats];
 // In host code the array's name is only a handle for the runtime, not a device address; the real address is looked
 // up once per device and kept here.
-static float* g_ln_bwd_partials_addr[64] = {};
+// After a device's first call the lookup is one atomic load: no lock is taken, so a caller that must never block on
+// one (the reason this entry point exists) is safe from its second call on; the mutex only serialises first calls.
+static std::atomic<float*> g_ln_bwd_partials_addr[kMaxDevices] = {};
 static std::mutex g_ln_bwd_partials_mu;
 
 static int noalloc_scratch(int device, float** out) {
-    GCB_REQUIRE(device >= 0 && device < 64, "gcb_layernorm_bwd_noalloc_f32: device index %d is outside the supported range", device);
-    std::lock_guard<std::mutex> lk(g_ln_bwd_partials_mu);
-    if (!g_ln_bwd_partials_addr[device]) {
-        GCB_CHECK_CUDA(cudaSetDevice(device));
-        float* p = nullptr;
-        GCB_CHECK_CUDA(cudaGetSymbolAddress((void**)&p, g_ln_bwd_partials));
-        g_ln_bwd_partials_addr[device] = p;
+    GCB_REQUIRE(device >= 0 && device < kMaxDevices, "gcb_layernorm_bwd_noalloc_f32: device index %d is outside the supported range", device);
+    float* p = g_ln_bwd_partials_addr[device].load(std::memory_order_acquire);
+    if (!p) {
+        std::lock_guard<std::mutex> lk(g_ln_bwd_partials_mu);
+        p = g_ln_bwd_partials_addr[device].load(std::memory_order_relaxed);
+        if (!p) {
+            GCB_CHECK_CUDA(cudaSetDevice(device));
+            GCB_CHECK_CUDA(cudaGetSymbolAddress((void**)&p, g_ln_bwd_partials));
+            g_ln_bwd_partials_addr[device].store(p, std::memory_order_release);
+        }
     }
-    *out = g_ln_bwd_partials_addr[device];
+    *out = p;
     return GCB_OK;
 }
 
@@ -547,9 +556,16 @@ extern "C" {
 int gcb_layernorm_bwd_noalloc_f32(gcb_ctx* ctx, float* dx, float* dgamma, float* dbeta, const float* dy, const float* x, const float* gamma, const float* mean, const float* rstd,
                                   int64_t rows, int64_t cols, int acc_dx, int acc_params) {
     GCB_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (dy && x && gamma && mean && rstd)), "gcb_layernorm_bwd_noalloc_f32: bad arguments");
-    GCB_REQUIRE(cols > 0 && rows > 0, "gcb_layernorm_bwd_noalloc_f32: empty input (rows %lld, cols %lld)", (long long)rows, (long long)cols);
+    if (cols == 0) return GCB_OK;
     GCB_REQUIRE(cols <= kNoAllocMaxCols && cols % 4 == 0,
                 "gcb_layernorm_bwd_noalloc_f32: cols = %lld is beyond what the fixed scratch array covers (multiples of 4 up to %d); use gcb_layernorm_bwd_f32", (long long)cols, kNoAllocMaxCols);
+    if (rows == 0) {  // as gcb_layernorm_bwd_f32: an empty batch contributes zero parameter gradients
+        if (!acc_params) {
+            if (dgamma) GCB_CHECK_CUDA(cudaMemsetAsync(dgamma, 0, sizeof(float) * cols, ctx->stream));
+            if (dbeta) GCB_CHECK_CUDA(cudaMemsetAsync(dbeta, 0, sizeof(float) * cols, ctx->stream));
+        }
+        return GCB_OK;
+    }
     GCB_REQUIRE(aligned16(x) && aligned16(dy) && aligned16(gamma) && (dx == nullptr || aligned16(dx)), "gcb_layernorm_bwd_noalloc_f32: x, dy, gamma and dx must be 16-byte aligned");
     float* scratch = nullptr;
     int rc = noalloc_scratch(ctx->device, &scratch);

@@ -59,7 +59,9 @@ GCB_API int gcb_ctx_create_on_stream(int device, void* cuda_stream, gcb_ctx** ou
 GCB_API int gcb_ctx_destroy(gcb_ctx* ctx);
 GCB_API void* gcb_ctx_stream(gcb_ctx* ctx);
 GCB_API int gcb_ctx_device(gcb_ctx* ctx);
-GCB_API int gcb_ctx_sync(gcb_ctx* ctx); /* cudaStreamSynchronize + sticky-error check */
+/* cudaStreamSynchronize + check of the device status word: GCB_TIMEOUT when a kernel gave up on a bounded wait,
+ * GCB_INVALID_ARG when an index or target outside its table was skipped.  gcb_copy_d2h performs the same check. */
+GCB_API int gcb_ctx_sync(gcb_ctx* ctx);
 /* Failure-path self-test (no counterpart in the reference, whose kernels never wait on one another): launches a
  * one-thread kernel that waits on a barrier nothing completes, gives up after max_polls polls of about 20 us each and
  * records that in the context's status word, exactly as every bounded wait of the GEMM and norm kernels does.  The next
@@ -67,6 +69,10 @@ GCB_API int gcb_ctx_sync(gcb_ctx* ctx); /* cudaStreamSynchronize + sticky-error 
 GCB_API int gcb_selftest_bounded_wait(gcb_ctx* ctx, int max_polls);
 /* Number of kernels this library launched through ctx since creation. */
 GCB_API int64_t gcb_ctx_launch_count(gcb_ctx* ctx);
+/* Launches whose kernel-family name starts with `prefix` (for tests and benches that assert which code path ran).  Families:
+ * gemm_tc_pair[_gelu_fwd|_gelu_bwd], gemm_tc_256[_softmax_bwd], gemm_tc_128, gemm_tc_64, splitk_reduce, gemm_simt,
+ * layernorm_bwd_ring, layernorm_bwd_warp, rmsnorm_bwd_ring, ..., one per entry point otherwise. */
+GCB_API int64_t gcb_ctx_launch_count_named(gcb_ctx* ctx, const char* prefix);
 /* Which GEMM engine ran last: 0 none, 1 SIMT fp32, 2 tcgen05 (split fp32). */
 GCB_API int gcb_ctx_last_gemm_engine(gcb_ctx* ctx);
 /* Force the GEMM engine: 0 auto, 1 SIMT fp32 only, 2 tcgen05 only (fails where it cannot run). */
@@ -95,7 +101,7 @@ GCB_API int gcb_arena_set_limit(gcb_ctx* ctx, size_t bytes);
 
 /* ---- copies: Storage ctor / ToNode / Tensor::item, core/storage.hpp:64-68, memory_nodes.hpp:212-317 */
 GCB_API int gcb_copy_h2d(gcb_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);        /* synchronous */
-GCB_API int gcb_copy_d2h(gcb_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);        /* synchronous */
+GCB_API int gcb_copy_d2h(gcb_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);        /* synchronous; reports the status word like gcb_ctx_sync */
 GCB_API int gcb_copy_h2d_async(gcb_ctx* ctx, void* dst_dev, const void* src_pinned, size_t bytes); /* on the compute stream */
 GCB_API int gcb_copy_d2h_async(gcb_ctx* ctx, void* dst_pinned, const void* src_dev, size_t bytes);
 GCB_API int gcb_copy_d2d(gcb_ctx* ctx, void* dst, const void* src, size_t bytes);
@@ -134,8 +140,9 @@ GCB_API int gcb_sum_squares_f32(gcb_ctx* ctx, float* out_scalar, const float* in
  * Row-major C[M,N] = alpha * op(A)[M,K] * op(B)[K,N] + beta * C, leading dimensions in elements,
  * exactly the fields of NMMMeta / BMMMeta (gradc/core/types.hpp:118-158).
  * bias (optional, length N) is added to every row — it folds the AddNode that follows each Linear
- * matmul (nn/layers/linear.hpp:23).  fp32 accuracy: tcgen05 kind::tf32 issued three times on
- * split operands (3xTF32) or the SIMT fp32 engine for shapes TMA cannot address. */
+ * matmul (nn/layers/linear.hpp:23).  fp32-class accuracy: tcgen05 on split operands — by default one kind::tf32 product
+ * of the truncated parts plus two kind::f16 (BF16) cross products, see gcb_ctx_set_gemm_split_mode — or the SIMT fp32 engine
+ * for shapes TMA cannot address. */
 GCB_API int gcb_gemm_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda,
                  const float* B, int64_t ldb, float beta, float* C, int64_t ldc, const float* bias);
 /* Batched with two-level batch strides (batch index = outer * batch_inner + inner) so that head-sliced
@@ -221,8 +228,9 @@ GCB_API int gcb_layernorm_bwd_f32(gcb_ctx* ctx, float* dx /*opt*/, float* dgamma
  * Same arithmetic, kernels and results as gcb_layernorm_bwd_f32, but the per-CTA dgamma / dbeta partial sums live in a
  * fixed 3.5 MiB device array that is part of the library image (every GPU that loads the library holds it until the
  * process exits) instead of in the context's arena; the call performs no cudaMalloc, cudaFree or arena operation.
- * Limits: cols must be a multiple of 4 and at most 1024, rows >= 1, x / dy / gamma / dx 16-byte aligned; anything else
- * is rejected with GCB_INVALID_ARG.
+ * Limits: cols must be a multiple of 4 and at most 1024, x / dy / gamma / dx 16-byte aligned; anything else is rejected
+ * with GCB_INVALID_ARG.  rows == 0 behaves as in gcb_layernorm_bwd_f32 (dgamma / dbeta zeroed unless accumulating).
+ * From its second call on a device the entry point takes no host lock either (the address lookup is one atomic load).
  * The first call on each device looks up the array's device address (one runtime query, no allocation); make that
  * first call before starting any stream capture.  All calls share the one array, which keeps whatever the previous call
  * left in it; each call overwrites the part it reads, so nothing needs clearing, but two calls that overlap on the GPU

@@ -10,10 +10,10 @@
 #   4. `<corecrt_malloc.h>` / `<cblas.h>`                       -> two shim headers
 # None of the patches touches arithmetic.  Outputs go to oracle/_ref/ only.
 #
-# Usage: oracle/build_ref.sh [reference_root]     (default /root/reference)
+# Usage: oracle/build_ref.sh [reference_root]     (default: $GRADC_REFERENCE_ROOT, else a `reference` directory beside this repository)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${GRADC_REFERENCE_ROOT:-$HERE/../../reference}}"
 OUT="$HERE/_ref"
 if [ ! -d "$REF/gradc" ]; then
   echo "build_ref: reference tree not found at $REF (prebuilt oracle/_ref is used as is)"; exit 0

@@ -60,10 +60,28 @@ def run_ops(tmp):
 
 GPT_CASES = {
     # name: arch, V, T, C, H, L, F, B, steps, accum, clip, perturb
-    "config1_lngelu": ("lngelu", 512, 64, 128, 4, 2, 512, 4, 10, 1, 0.0, False),  # BASELINE config 1
+    "config1_lngelu": ("lngelu", 512, 64, 128, 4, 2, 512, 4, 10, 1, 0.0, False),  # the reference-runnable tiny GPT: 2 layers, d_model 128
     "mini_lngelu": ("lngelu", 96, 16, 32, 4, 2, 80, 3, 3, 2, 1.0, True),
     "mini_rmsswiglu": ("rmsswiglu", 96, 16, 32, 4, 2, 96, 3, 3, 2, 1.0, True),
+    # large enough that one step runs the kernels of the full-size model: 5120 rows x 256 / 1024 columns reach the CTA-pair
+    # GEMM with its GELU epilogues, split-K weight gradients, the 256-wide dS GEMM with the softmax-backward epilogue and the
+    # staged LayerNorm backward.  Stored as a digest (DIGEST_CASES) because the full tensors would be ~25 MB.
+    "mid_lngelu": ("lngelu", 1024, 256, 256, 4, 2, 1024, 20, 3, 1, 1.0, True),
 }
+DIGEST_CASES = {"mid_lngelu"}
+# Gradient tolerance of the last recorded step per case (default 1e-4, the bar of the first step everywhere).  At 5120 rows
+# the reference's own serial fp32 sums (bias / LayerNorm parameter gradients, sgemm over K = 5120) carry ~1e-4 of rounding
+# noise by the third step: the numpy restatement, which reduces in float64, reproduces the reference's weights after three
+# steps to 1.2e-7 and its first-step gradients to 2e-5, but differs from its third-step gradients by up to 1.07e-4.
+LAST_STEP_TOL = {"mid_lngelu": 3e-4}
+DIGEST_STRIDE = 29  # every 29th element of each flattened tensor is kept
+
+
+def digest(a):
+    """What a digest fixture keeps of one tensor: [sum, sum of squares, max |x|] in float64 and a fixed strided sample."""
+    flat = np.asarray(a, dtype=np.float32).reshape(-1)
+    f64 = flat.astype(np.float64)
+    return np.array([f64.sum(), (f64 * f64).sum(), np.abs(f64).max()], np.float64), flat[::DIGEST_STRIDE].copy()
 HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, wd=0.1, eps=1e-5, norm_eps=1e-5)
 
 
@@ -80,11 +98,18 @@ def run_gpt(tmp, name):
     subprocess.run(cmd, check=True)
     rows = np.loadtxt(prefix + "_loss.txt", dtype=np.float64).reshape(steps, 2)
     out = {"loss": rows[:, 0].astype(np.float32), "norm": rows[:, 1].astype(np.float32)}
+
+    def put(key, a):
+        if name in DIGEST_CASES:
+            out["stat/" + key], out["sample/" + key] = digest(a)
+        else:
+            out[key] = a
+
     for k in (1, steps):
         for n_, a in ckpt.load("%s_grads%d.ckpt" % (prefix, k)).items():
-            out["grads%d/%s" % (k, n_)] = a
+            put("grads%d/%s" % (k, n_), a)
     for n_, a in ckpt.load("%s_weights%d.ckpt" % (prefix, steps)).items():
-        out["weights%d/%s" % (steps, n_)] = a
+        put("weights%d/%s" % (steps, n_), a)
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
     print(name, "loss", out["loss"])
 
@@ -117,7 +142,12 @@ if __name__ == "__main__":
         sys.exit(0)
     if not os.path.exists(HARNESS):
         sys.exit("oracle/_ref/ref_harness missing: run oracle/build_ref.sh first")
+    only = [a[len("--only="):] for a in sys.argv if a.startswith("--only=")]
     with tempfile.TemporaryDirectory() as tmp:
+        if only:
+            for name in only:
+                run_gpt(tmp, name)
+            sys.exit(0)
         run_ops(tmp)
         for name in GPT_CASES:
             run_gpt(tmp, name)

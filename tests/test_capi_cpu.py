@@ -50,7 +50,9 @@ def test_reference_train_cpp_compiles_unchanged_against_the_host_api(tmp_path):
     import shutil
     import subprocess
 
-    src = "/root/reference/train.cpp"
+    from gradcraft_b200.build import reference_root
+
+    src = os.path.join(reference_root() or "", "train.cpp")
     if not os.path.exists(src):
         pytest.skip("reference tree not present on this machine")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

@@ -311,3 +311,117 @@ def test_fused_entry_points_accept_empty_problems_and_reject_bad_arguments(env):
     with pytest.raises(capi.GcbError) as e:
         ctx.ctx_set_gemm_split_mode(7)
     assert e.value.status == capi.INVALID_ARG
+
+
+def test_causal_attention_gemms_over_several_scheduling_groups(env):
+    """The six attention GEMMs of a training step on 80 heads of 1024 x 64: the 64-wide causal kernels deal their tiles in
+    groups of 2 x 148 / 8 = 37 heads (snake order inside a group), so 80 heads make two full groups and a ragged last one of
+    6, with the persistent loop rounded up past the last item.  Heads from the first group, a group boundary and the tail are
+    checked against float64 (full tensors would take minutes on the host)."""
+    ctx, torch, capi = env
+    Bn, H, T, D = 5, 16, 1024, 64
+    C = H * D
+    scale = 0.125
+    q, k, v, do = rnd(80, Bn, T, C), rnd(81, Bn, T, C), rnd(82, Bn, T, C), rnd(83, Bn, T, C) * 1e-2
+    Q, Kd, Vd, dO = (torch.from_numpy(x).cuda() for x in (q, k, v, do))
+    head = lambda a, i: a[i // H, :, (i % H) * D:(i % H + 1) * D].astype(np.float64)   # (T, D) of batch item i
+    low = np.tril(np.ones((T, T), bool))
+    blk = (np.arange(T)[:, None] // 128) == (np.arange(T)[None, :] // 128)
+    sample = [0, 1, 36, 37, 38, 73, 74, 75, 79]
+    # forward: scores (causal 1) -> band softmax -> P V (causal 2), as SDPANode::realize issues them
+    S = torch.full((Bn * H, T, T), float("nan"), device="cuda")
+    ctx.gemm_batched_causal_f32(0, 1, T, T, D, 1.0, Q, C, T * C, D, Kd, C, T * C, D, 0.0, S, T, H * T * T, T * T, Bn, H, 1)
+    ctx.sync()
+    assert ctx.ctx_last_gemm_engine() == 2
+    for i in sample:
+        ref = head(q, i) @ head(k, i).T
+        got = S[i].cpu().numpy()
+        assert float(np.abs(got[low] - ref[low]).max() / np.abs(ref).max()) < TOL, i
+    ctx.causal_softmax_fwd_band_f32(S, S, scale, Bn * H * T, T, 128)
+    Oo = torch.full((Bn, T, C), float("nan"), device="cuda")
+    ctx.gemm_batched_causal_f32(0, 0, T, D, T, 1.0, S, T, H * T * T, T * T, Vd, C, T * C, D, 0.0, Oo, C, T * C, D, Bn, H, 2)
+    ctx.sync()
+    o_host = Oo.cpu().numpy()
+    assert np.isfinite(o_host).all()
+    probs = {}
+    for i in sample:
+        s = np.where(low, head(q, i) @ head(k, i).T * scale, -np.inf)
+        p = np.exp(s - s.max(-1, keepdims=True))
+        p /= p.sum(-1, keepdims=True)
+        probs[i] = p
+        got_p = S[i].cpu().numpy()
+        assert float(np.abs(np.where(low, got_p, 0) - p).max()) < 1e-5, i
+        assert max_abs_rel(o_host[i // H, :, (i % H) * D:(i % H + 1) * D], p @ head(v, i)) < TOL, i
+    # backward: dV = P^T dO (causal 3), dS from the dP GEMM with the softmax backward in its epilogue, dQ = dS K (causal 2), dK = dS^T Q (causal 3)
+    dV, dQ, dK = (torch.full((Bn, T, C), float("nan"), device="cuda") for _ in range(3))
+    ctx.gemm_batched_causal_f32(1, 0, T, D, T, 1.0, S, T, H * T * T, T * T, dO, C, T * C, D, 0.0, dV, C, T * C, D, Bn, H, 3)
+    rd = torch.empty(Bn * H * T, device="cuda")
+    ctx.rowdot_batched_f32(rd, dO, C, T * C, D, Oo, C, T * C, D, T, D, Bn, H)
+    dS = torch.full((Bn * H, T, T), float("nan"), device="cuda")
+    ctx.gemm_batched_softmax_bwd_f32(0, 1, T, D, 1.0, dO, C, T * C, D, Vd, C, T * C, D, dS, T, H * T * T, T * T, Bn, H, S, rd, scale)
+    ctx.gemm_batched_causal_f32(0, 0, T, D, T, 1.0, dS, T, H * T * T, T * T, Kd, C, T * C, D, 0.0, dQ, C, T * C, D, Bn, H, 2)
+    ctx.gemm_batched_causal_f32(1, 0, T, D, T, 1.0, dS, T, H * T * T, T * T, Q, C, T * C, D, 0.0, dK, C, T * C, D, Bn, H, 3)
+    ctx.sync()
+    dv_h, dq_h, dk_h = dV.cpu().numpy(), dQ.cpu().numpy(), dK.cpu().numpy()
+    assert np.isfinite(dv_h).all() and np.isfinite(dq_h).all() and np.isfinite(dk_h).all()
+    for i in sample:
+        p = probs[i]
+        dp = head(do, i) @ head(v, i).T
+        ds = scale * p * (dp - (dp * p).sum(-1, keepdims=True))
+        got = dS[i].cpu().numpy()
+        assert float(np.abs(got[low] - ds[low]).max() / np.abs(ds).max()) < TOL, i
+        assert np.all(got[blk & ~low] == 0), i
+        sl = (i // H, slice(None), slice((i % H) * D, (i % H + 1) * D))
+        assert max_abs_rel(dv_h[sl], p.T @ head(do, i)) < TOL, i
+        assert max_abs_rel(dq_h[sl], ds @ head(k, i)) < TOL, i
+        assert max_abs_rel(dk_h[sl], ds.T @ head(q, i)) < TOL, i
+
+
+def test_fused_epilogues_take_the_scalar_path_for_side_arrays_off_a_16_byte_boundary(env):
+    """The epilogues read the probabilities / pre-activations and write the activations with 16-byte vector accesses only when
+    those arrays sit on 16-byte boundaries like C; a side array at a 4-byte offset must give the same result through the
+    scalar path (not a misaligned-address fault)."""
+    ctx, torch, capi = env
+    Bn, H, T, D = 1, 2, 256, 64
+    C = H * D
+    scale = 0.125
+    v, do = rnd(90, Bn, T, C), rnd(91, Bn, T, C) * 1e-2
+    p = np.tril(np.abs(rnd(92, Bn * H, T, T)))
+    p = (p / p.sum(-1, keepdims=True)).astype(np.float32)
+    rdot = rnd(93, Bn * H * T) * 1e-2
+    buf = torch.zeros(p.size + 4, device="cuda")
+    P_off = buf[1:1 + p.size]
+    P_off.copy_(torch.from_numpy(p.reshape(-1)))
+    assert P_off.data_ptr() % 16 == 4
+    dO, Vd, RD = torch.from_numpy(do).cuda(), torch.from_numpy(v).cuda(), torch.from_numpy(rdot).cuda()
+    dS = torch.full((Bn * H, T, T), float("nan"), device="cuda")
+    ctx.gemm_batched_softmax_bwd_f32(0, 1, T, D, 1.0, dO, C, T * C, D, Vd, C, T * C, D, dS, T, H * T * T, T * T, Bn, H, P_off, RD, scale)
+    ctx.sync()
+    heads = lambda a: a.reshape(Bn, T, H, D).transpose(0, 2, 1, 3).astype(np.float64).reshape(Bn * H, T, D)
+    dp = heads(do) @ heads(v).transpose(0, 2, 1)
+    ref = scale * p.astype(np.float64) * (dp - rdot.astype(np.float64).reshape(Bn * H, T, 1))
+    low = np.tril(np.ones((T, T), bool))
+    got = dS.cpu().numpy()
+    assert float(np.abs(got[:, low] - ref[:, low]).max() / np.abs(ref).max()) < TOL
+    # GELU epilogues of the CTA-pair kernel with pre / act at a 4-byte offset
+    M, N, K = 512, 512, 256
+    x, W, bias = rnd(94, M, K), rnd(95, K, N) * 0.1, rnd(96, N)
+    pre = torch.empty(M, N, device="cuda")
+    abuf = torch.zeros(M * N + 4, device="cuda")
+    act_off = abuf[1:1 + M * N]
+    ctx.linear_gelu_fwd_f32(0, M, N, K, torch.from_numpy(x).cuda(), K, torch.from_numpy(W).cuda(), N, torch.from_numpy(bias).cuda(), pre, act_off)
+    again = torch.empty_like(pre)
+    ctx.gelu_fwd_f32(again, pre, M * N)
+    ctx.sync()
+    assert max_abs_rel(pre.cpu().numpy(), x.astype(np.float64) @ W.astype(np.float64) + bias) < 1e-5
+    assert torch.equal(again.reshape(-1), act_off)
+    pbuf = torch.zeros(M * N + 4, device="cuda")
+    pre_off = pbuf[1:1 + M * N]
+    pre_off.copy_(pre.reshape(-1))
+    dy, W2 = rnd(97, M, K) * 1e-2, rnd(98, N, K)
+    out_a, out_b = torch.empty(M, N, device="cuda"), torch.empty(M, N, device="cuda")
+    ctx.gemm_gelu_bwd_f32(0, 1, M, N, K, torch.from_numpy(dy).cuda(), K, torch.from_numpy(W2).cuda(), K, pre, out_a)
+    ctx.gemm_gelu_bwd_f32(0, 1, M, N, K, torch.from_numpy(dy).cuda(), K, torch.from_numpy(W2).cuda(), K, pre_off, out_b)
+    ctx.sync()
+    assert ctx.ctx_launch_count_named(b"gemm_tc_pair_gelu_bwd") >= 2
+    assert torch.equal(out_a, out_b)

@@ -329,9 +329,51 @@ def test_layernorm_rmsnorm_vs_oracle(env, rows, cols):
     assert max_abs_rel(host(ctx, y), ry) < TOL and max_abs_rel(host(ctx, dx), rdx) < TOL and max_abs_rel(host(ctx, dg), rdg) < TOL
 
 
-def test_layernorm_bwd_is_deterministic(env):
+@pytest.mark.parametrize("rows,cols", [(8192, 1024), (5000, 768), (4736, 256), (6001, 512), (4800, 128)])
+def test_norm_backward_staged_kernel_vs_oracle(env, rows, cols):
+    """Row counts from 4 x 148 x 8 = 4736 up select the persistent kernel that stages rows through shared memory with bulk
+    async copies (the LayerNorm / RMSNorm backward of every benchmarked shape).  It is held to the numpy oracle here with both
+    accumulate flags, with dx left out, and with a row count that leaves the last sweep of the warps ragged."""
     ctx, torch, capi = env
-    rows, cols = 4096, 1024
+    x, dy = rnd(120, rows, cols) * 2 + 0.3, rnd(121, rows, cols, scale=1e-2)
+    g, b = rnd(122, cols) * 0.2 + 1, rnd(123, cols) * 0.1
+    X, DY, G, Bt = dev(torch, x), dev(torch, dy), dev(torch, g), dev(torch, b)
+    y, s0, s1 = torch.empty(rows, cols, device="cuda"), torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    # LayerNorm
+    ctx.layernorm_fwd_f32(y, s0, s1, X, G, Bt, rows, cols, 1e-5)
+    ry, mu, rs = O.layernorm_fwd(x, g, b, 1e-5)
+    rdx, rdg, rdb = O.layernorm_bwd(dy, x, g, mu, rs)
+    dx, dg, db = torch.full((rows, cols), 7.0, device="cuda"), torch.full((cols,), 7.0, device="cuda"), torch.full((cols,), 7.0, device="cuda")
+    ctx.layernorm_bwd_f32(dx, dg, db, DY, X, G, s0, s1, rows, cols, 0, 0)
+    assert max_abs_rel(host(ctx, y), ry) < TOL
+    assert max_abs_rel(host(ctx, dx), rdx) < TOL and max_abs_rel(host(ctx, dg), rdg) < TOL and max_abs_rel(host(ctx, db), rdb) < TOL
+    ctx.layernorm_bwd_f32(dx, dg, db, DY, X, G, s0, s1, rows, cols, 1, 0)   # dx accumulates, parameters overwrite
+    assert max_abs_rel(host(ctx, dx), 2 * rdx) < TOL and max_abs_rel(host(ctx, dg), rdg) < TOL and max_abs_rel(host(ctx, db), rdb) < TOL
+    ctx.layernorm_bwd_f32(dx, dg, db, DY, X, G, s0, s1, rows, cols, 0, 1)   # dx overwrites, parameters accumulate
+    assert max_abs_rel(host(ctx, dx), rdx) < TOL and max_abs_rel(host(ctx, dg), 2 * rdg) < TOL and max_abs_rel(host(ctx, db), 2 * rdb) < TOL
+    dg2, db2 = torch.full((cols,), 7.0, device="cuda"), torch.full((cols,), 7.0, device="cuda")
+    ctx.layernorm_bwd_f32(None, dg2, db2, DY, X, G, s0, s1, rows, cols, 0, 0)  # parameter gradients only
+    assert max_abs_rel(host(ctx, dg2), rdg) < TOL and max_abs_rel(host(ctx, db2), rdb) < TOL
+    dx2 = torch.full((rows, cols), 7.0, device="cuda")
+    ctx.layernorm_bwd_f32(dx2, None, None, DY, X, G, s0, s1, rows, cols, 0, 0)  # dx only
+    assert max_abs_rel(host(ctx, dx2), rdx) < TOL
+    # RMSNorm
+    ctx.rmsnorm_fwd_f32(y, s0, X, G, rows, cols, 1e-5)
+    ry, inv = O.rmsnorm_fwd(x, g, 1e-5)
+    rdx, rdg = O.rmsnorm_bwd(dy, x, g, inv)
+    dx.fill_(7.0); dg.fill_(7.0)
+    ctx.rmsnorm_bwd_f32(dx, dg, DY, X, G, s0, rows, cols, 0, 0)
+    assert max_abs_rel(host(ctx, y), ry) < TOL and max_abs_rel(host(ctx, dx), rdx) < TOL and max_abs_rel(host(ctx, dg), rdg) < TOL
+    ctx.rmsnorm_bwd_f32(dx, dg, DY, X, G, s0, rows, cols, 1, 1)
+    assert max_abs_rel(host(ctx, dx), 2 * rdx) < TOL and max_abs_rel(host(ctx, dg), 2 * rdg) < TOL
+    ctx.rmsnorm_bwd_f32(None, dg, DY, X, G, s0, rows, cols, 0, 0)
+    assert max_abs_rel(host(ctx, dg), rdg) < TOL
+
+
+@pytest.mark.parametrize("rows", [4096, 16384])
+def test_layernorm_bwd_is_deterministic(env, rows):
+    ctx, torch, capi = env
+    cols = 1024  # 4096 rows: warp-per-row kernel; 16384 rows: the staged persistent kernel
     x, dy, g = rnd(30, rows, cols), rnd(31, rows, cols, scale=1e-2), rnd(32, cols) + 1
     X, DY, G = dev(torch, x), dev(torch, dy), dev(torch, g)
     mu, rs = dev(torch, x.mean(1)), dev(torch, 1 / np.sqrt(x.var(1) + 1e-5))

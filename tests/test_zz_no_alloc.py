@@ -2,13 +2,14 @@
 block on an allocator lock, or an embedding application that owns all device memory).  It keeps its scratch in a fixed
 device array inside the library instead of taking a block from the context's arena.
 
-Checked here, through the C ABI: it gives the same dx / dgamma / dbeta as gcb_layernorm_bwd_f32 on two calls in a row
-with different inputs and sizes (the shared array keeps the previous call's contents, which must not leak into the next
+Checked here, through the C ABI: it gives the same dx / dgamma / dbeta as gcb_layernorm_bwd_f32 and as the numpy oracle on
+two calls in a row with different inputs and sizes (the shared array keeps the previous call's contents, which must not leak into the next
 result), it leaves the arena untouched, and it refuses sizes its array cannot hold.  This file sorts last so that a run
 stopping at the first failure has already executed every other test."""
 import numpy as np
 import pytest
 
+from oracle import numpy_oracle as O
 from tests.helpers import max_abs_rel
 
 pytestmark = pytest.mark.gpu
@@ -41,6 +42,10 @@ def test_noalloc_layernorm_bwd_matches_arena_version_twice():
             assert (ctx.arena_in_use_bytes(), ctx.arena_reserved_bytes(), ctx.arena_high_water_bytes()) == (in_use, reserved, hwm)
             for a, r in zip(got, ref):
                 assert max_abs_rel(a.cpu().numpy(), r.cpu().numpy()) < TOL
+            # and the independent checker: the numpy restatement of the reference's LayerNorm backward
+            _, o_mu, o_rs = O.layernorm_fwd(x, g, b, 1e-5)
+            for a, r in zip(got, O.layernorm_bwd(dy, x, g, o_mu, o_rs)):
+                assert max_abs_rel(a.cpu().numpy(), r) < TOL
             # accumulate flags behave the same way
             ctx.layernorm_bwd_noalloc_f32(got[0], got[1], got[2], DY, X, G, mu, rs, rows, cols, 1, 1)
             ctx.sync()
