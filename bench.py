@@ -14,9 +14,15 @@ Prints one JSON line (rank 0):
             the loss inside the timed region;
   roofline  the GEMM engine (dominant kernel): algorithmic FLOP/s over the launches of the timed region vs the measured
             dense tensor peak;
-  cpu_baseline  the reference's own CPU path (oracle/_ref) timed on the host cores on a bounded sample.
-`--impl reference` times that CPU path alone on the same metric.
-`--workload kernels` reports the fused backward kernels of the microbenchmark configuration against the HBM roofline.
+  kernels   (1 GPU) every bandwidth-bound backward / optimizer kernel at the microbenchmark shapes: achieved HBM GB/s over the
+            measured copy peak ("bwd kernel % HBM peak", the second half of the metric);
+  reference_cuda / vs_reference_cuda  (1 GPU) the reference's own CUDA path built for sm_100a, same model and batch, and
+            value over it;
+  cpu_baseline  the reference's own CPU path (oracle/_ref) timed on the host cores on a bounded sample;
+  dp        (N > 1) exposed communication time per step, GEMM time per step with NCCL in flight, and whether every rank
+            ends with bit-identical weights.
+`--impl reference` times the reference's CPU path alone on the same metric; `--impl reference-cuda` its CUDA path.
+`--workload kernels` prints the kernel table alone, `--workload gemm` every GEMM shape of the step.
 """
 import argparse
 import json
@@ -30,6 +36,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+TRAFFIC_PROFILE = "gemm_tc_pair_kernel_linear_fwd_32768x1024x1024.md"
 WORKLOADS = {
     # name: arch, V, T, C, H, L, F, B per GPU, micro-batches per step
     "gpt180m": ("lngelu", 32768, 1024, 1024, 16, 12, 4096, 32, 1),
@@ -37,6 +44,7 @@ WORKLOADS = {
     "tiny": ("lngelu", 512, 64, 128, 4, 2, 512, 4, 1),
 }
 HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, wd=0.1, eps=1e-5, norm_eps=1e-5, ce_eps=1e-5)
+CLIP = 1.0  # GlobalNormClipper threshold, as train.cpp:158 of the reference runs it: the clip is part of the timed step
 
 
 def peaks():
@@ -45,6 +53,19 @@ def peaks():
         d = json.load(open(p))
         return dict(hbm_gbs=d["hbm_gbs"], tensor_tflops=d.get("bf16_tflops_sustained", d["bf16_tflops"]), tensor_tflops_burst=d["bf16_tflops"], source="measured")
     return dict(hbm_gbs=6650.0, tensor_tflops=1400.0, tensor_tflops_burst=1590.0, source="fallback")
+
+
+def profile_traffic(name):
+    """DRAM read + write bytes of one captured launch, from the table row `dram__bytes_read.sum + dram__bytes_write.sum | a MB + b MB = c MB`
+    of a committed ncu summary under profiles/ (None when the file or the row is missing)."""
+    import re
+
+    try:
+        text = open(os.path.join(ROOT, "profiles", name)).read()
+    except OSError:
+        return None
+    m = re.search(r"dram__bytes_read\.sum \+ dram__bytes_write\.sum\s*\|\s*[\d.]+ MB \+ [\d.]+ MB = ([\d.]+) MB", text)
+    return float(m.group(1)) * 1e6 if m else None
 
 
 def flops_per_token(V, T, C, L, F):
@@ -95,79 +116,104 @@ class ClockSampler:
 
 
 # ---- reference CPU arm -------------------------------------------------------------------------------------
-def reference_cpu_run(workload, steps, warmup, sample_B=1):
-    """Times oracle/_ref/ref_harness (GradCraft's CPUBackend + OpenBLAS) on `steps` steps of a bounded sample:
-    the workload's model and sequence length with sample_B sequences per step.  Returns (tokens/s, description)."""
+CPU_SAMPLE_T = 256  # tokens per CPU step: one sequence cut to 256 tokens (~4 s of host work per step for gpt180m on 16 cores)
+
+
+def reference_cpu_run(workload, steps, warmup, sample_B=1, sample_T=None):
+    """Times oracle/_ref/ref_harness (GradCraft's CPUBackend + OpenBLAS) on exactly `warmup` untimed + `steps` timed steps of a
+    bounded sample: the workload's model with its seeded weights, sample_B sequences of sample_T tokens per step.
+    Returns (tokens/s, cores, description, kind, ms per timed step)."""
     arch, V, T, C, H, L, F, B, accum = WORKLOADS[workload]
+    sample_T = min(T, sample_T or CPU_SAMPLE_T)
     harness = os.path.join(ROOT, "oracle", "_ref", "ref_harness")
     cores = os.cpu_count() or 1
     if not os.path.exists(harness):
-        return None, cores, "oracle/_ref/ref_harness is not built", "reference"
+        return None, cores, "oracle/_ref/ref_harness is not built", "reference", None
     import numpy as np
 
     from gradcraft_b200 import synth
+    from oracle import ckpt
 
     n_steps = steps + warmup
     with tempfile.TemporaryDirectory() as tmp:
-        synth.token_batches(99, n_steps, sample_B, T, V).tofile(os.path.join(tmp, "tok.i64"))
+        # the harness reads T tokens per sequence from the file only when it runs full sequences; with a shorter sample it reads sample_T
+        synth.token_batches(99, n_steps, sample_B, sample_T, V).tofile(os.path.join(tmp, "tok.i64"))
+        ckpt.save(os.path.join(tmp, "w.ckpt"), synth.gpt_weights(arch, V, T, C, H, L, F, seed=0))  # the weights the GPU arm trains from
         h = HYPER
-        cmd = [harness, "gpt", arch] + [str(v) for v in (V, T, C, H, L, F, sample_B, n_steps, 1, h["lr"], h["beta1"], h["beta2"], h["wd"], h["eps"], 0.0)]
-        cmd += ["-", os.path.join(tmp, "tok.i64"), os.path.join(tmp, "out"), str(h["norm_eps"])]
-        env = dict(os.environ, REF_BLAS_THREADS=str(cores), OPENBLAS_NUM_THREADS=str(cores))
+        cmd = [harness, "gpt", arch] + [str(v) for v in (V, T, C, H, L, F, sample_B, n_steps, 1, h["lr"], h["beta1"], h["beta2"], h["wd"], h["eps"], CLIP)]
+        cmd += [os.path.join(tmp, "w.ckpt"), os.path.join(tmp, "tok.i64"), os.path.join(tmp, "out"), str(h["norm_eps"])]
+        env = dict(os.environ, REF_BLAS_THREADS=str(cores), OPENBLAS_NUM_THREADS=str(cores), REF_HARNESS_NO_DUMP="1", REF_HARNESS_SAMPLE_T=str(sample_T))
         r = subprocess.run(cmd, env=env, capture_output=True, text=True)
         if r.returncode != 0:
-            return None, cores, "ref_harness failed: " + (r.stderr.strip().splitlines() or ["?"])[-1], "reference"
+            return None, cores, "ref_harness failed: " + (r.stderr.strip().splitlines() or ["?"])[-1], "reference", None
         ms = np.loadtxt(os.path.join(tmp, "out_time.txt"), ndmin=1)
-    ms = ms[warmup:] if len(ms) > warmup else ms
-    tok_s = sample_B * T / (float(np.mean(ms)) / 1e3)
-    desc = "%s model, %d sequence(s) of %d tokens per step, %d timed steps, weights at their init defaults (zeros / gamma=1), OpenBLAS threads=%d, elementwise code single-threaded" % (
-        workload, sample_B, T, len(ms), cores)
-    return tok_s, cores, desc, "reference"
+    ms = ms[warmup:]
+    ms_step = float(np.mean(ms))
+    tok_s = sample_B * sample_T / (ms_step / 1e3)
+    desc = "%s model with the GPU arm's seeded weights, %d sequence(s) of %d tokens per step (the model's sequence length is %d), %d warm-up + %d timed steps incl. clip and AdamW, OpenBLAS threads=%d, elementwise code single-threaded as the reference has it" % (
+        workload, sample_B, sample_T, T, warmup, len(ms), cores)
+    return tok_s, cores, desc, "reference", ms_step
 
 
-def run_reference_cuda_arm(args, rank):
-    """The reference's own CUDA path (its .cu files built for sm_100a by oracle/build_ref.sh) on one GPU: the figure the
-    "x times the reference's CUDA path" target is quoted against.  Not the contract's reference arm (that is the CPU path)."""
-    if rank != 0:
-        return
-    arch, V, T, C, H, L, F, B, accum = WORKLOADS[args.workload]
+def reference_cuda_run(workload, steps, warmup, batch=0):
+    """The reference's own CUDA path (its two .cu files built for sm_100a by oracle/build_ref.sh; cuBLAS in TF32 tensor-op mode as
+    the reference sets it) on the same model, batch size and token shapes, one GPU.  Returns a dict with `value` (tokens/s) or
+    `unavailable`."""
+    arch, V, T, C, H, L, F, B, accum = WORKLOADS[workload]
     harness = os.path.join(ROOT, "oracle", "_ref", "ref_harness_cuda")
     if not os.path.exists(harness):
-        print(json.dumps({"impl": "reference-cuda", "unavailable": "oracle/_ref/ref_harness_cuda is not built"}))
-        return
+        return {"unavailable": "oracle/_ref/ref_harness_cuda is not built"}
     from gradcraft_b200 import synth
 
-    Bs = args.ref_batch or B
+    Bs = batch or B
     with tempfile.TemporaryDirectory() as tmp:
         synth.token_batches(99, 1, Bs, T, V).tofile(os.path.join(tmp, "tok.i64"))
-        cmd = [harness, "gptcuda", arch] + [str(v) for v in (V, T, C, H, L, F, Bs, args.steps, args.warmup)] + [os.path.join(tmp, "tok.i64")]
+        cmd = [harness, "gptcuda", arch] + [str(v) for v in (V, T, C, H, L, F, Bs, steps, warmup)] + [os.path.join(tmp, "tok.i64")]
         t0 = time.time()
         r = subprocess.run(cmd, capture_output=True, text=True)
     out = [l for l in r.stdout.splitlines() if l.startswith("tokens_per_s")]
     if r.returncode != 0 or not out:
-        print(json.dumps({"impl": "reference-cuda", "unavailable": "ref_harness_cuda failed: " + ((r.stderr.strip().splitlines() or r.stdout.strip().splitlines() or ["?"])[-1])[:300]}))
-        return
+        return {"unavailable": "ref_harness_cuda failed: " + ((r.stderr.strip().splitlines() or r.stdout.strip().splitlines() or ["?"])[-1])[:300]}
     f = out[-1].split()
-    print(json.dumps({"impl": "reference-cuda", "metric": "GPT fp32 train tokens/s (fwd+bwd+AdamW)", "value": float(f[1]), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-                      "ms_per_step": float(f[3]), "higher_is_better": True, "dtype": "f32 (cuBLAS TF32 tensor-op mode, as the reference sets it)", "data": "synthetic Zipf(1.1) tokens, one fixed batch",
-                      "config": {"workload": args.workload, "arch": arch, "layers": L, "d_model": C, "heads": H, "d_ff": F, "seq_len": T, "vocab": V, "batch": Bs},
-                      "pool_high_water_gb": float(f[5]), "last_loss": float(f[7]), "wall_s": time.time() - t0}))
+    return {"value": float(f[1]), "unit": "tokens/s", "ms_per_step": float(f[3]), "steps": steps, "warmup": warmup, "batch": Bs, "pool_high_water_gb": float(f[5]), "last_loss": float(f[7]),
+            "wall_s": time.time() - t0, "what": "the reference's CUDA path (kernels_math.cu / kernels_utils.cu built with -O3 -use_fast_math for sm_100a, cuBLAS TF32 tensor-op GEMMs), "
+            "same model and batch, one fixed batch of synthetic tokens, wall clock around %d steps after %d warm-up" % (steps, warmup)}
+
+
+def run_reference_cuda_arm(args, rank):
+    if rank != 0:
+        return
+    arch, V, T, C, H, L, F, B, accum = WORKLOADS[args.workload]
+    res = reference_cuda_run(args.workload, args.steps, args.warmup, args.ref_batch)
+    if "unavailable" in res:
+        print(json.dumps({"impl": "reference-cuda", "unavailable": res["unavailable"]}))
+        return
+    print(json.dumps({"impl": "reference-cuda", "metric": "GPT fp32 train tokens/s (fwd+bwd+AdamW)", "value": res["value"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": res["ms_per_step"], "higher_is_better": True, "dtype": "f32 (cuBLAS TF32 tensor-op mode, as the reference sets it)", "data": "synthetic Zipf(1.1) tokens, one fixed batch",
+                      "config": {"workload": args.workload, "arch": arch, "layers": L, "d_model": C, "heads": H, "d_ff": F, "seq_len": T, "vocab": V, "batch": res["batch"]},
+                      "pool_high_water_gb": res["pool_high_water_gb"], "last_loss": res["last_loss"], "wall_s": res["wall_s"]}))
 
 
 def run_reference_arm(args, rank):
+    """The reference's CPU implementation on the host cores: exactly --warmup untimed and --steps timed steps, each a bounded
+    sample (one sequence cut to CPU_SAMPLE_T tokens); more steps than fit in about four minutes are cut and the line says so."""
     if rank != 0:
         return
     arch, V, T, C, H, L, F, B, accum = WORKLOADS[args.workload]
     t0 = time.time()
-    # each step is ~1.3 TFLOP of CPU work on the bounded sample: two timed steps after one warm-up keep the run within minutes
-    tok_s, cores, desc, kind = reference_cpu_run(args.workload, min(args.steps, 2), min(args.warmup, 1))
+    est_s = 4.5 * (flops_per_token(V, min(T, CPU_SAMPLE_T), C, L, F) * min(T, CPU_SAMPLE_T)) / (flops_per_token(32768, 256, 1024, 12, 4096) * 256)  # ~4.5 s per step for gpt180m on 16 cores
+    fit = max(1, int(240.0 / max(est_s, 1e-3)))
+    warm = min(args.warmup, max(1, fit // 5))
+    steps = max(1, min(args.steps, fit - warm))
+    tok_s, cores, desc, kind, ms_step = reference_cpu_run(args.workload, steps, warm)
     if tok_s is None:
         print(json.dumps({"impl": "reference", "unavailable": desc}))
         return
     line = {
-        "impl": "reference", "metric": "GPT fp32 train tokens/s (fwd+bwd+AdamW)", "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * T / tok_s, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic Zipf(1.1) tokens",
-        "config": {"workload": args.workload, "arch": arch, "layers": L, "d_model": C, "heads": H, "d_ff": F, "seq_len": T, "vocab": V, "sample": desc},
+        "impl": "reference", "metric": "GPT fp32 train tokens/s (fwd+bwd+AdamW)", "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+        "steps_requested": args.steps, "warmup_requested": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic Zipf(1.1) tokens, N(0,0.02) weights (seed 0)",
+        "config": {"workload": args.workload, "arch": arch, "layers": L, "d_model": C, "heads": H, "d_ff": F, "seq_len": T, "vocab": V, "clip": CLIP, "sample": desc},
         "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": desc},
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.time() - t0,
@@ -196,7 +242,7 @@ def run_ours(args, rank, world, local_rank):
     pk = peaks()
 
     tr = Trainer(arch, V, T, C, H, L, F, lr=HYPER["lr"], beta1=HYPER["beta1"], beta2=HYPER["beta2"], wd=HYPER["wd"], eps=HYPER["eps"], norm_eps=HYPER["norm_eps"], ce_eps=HYPER["ce_eps"],
-                 clip=0.0, device=local_rank)
+                 clip=CLIP, device=local_rank)
     tr.load(synth.gpt_weights(arch, V, T, C, H, L, F, seed=0))  # identical on every rank
     lib = capi.lib()
     ctx = tr.context()
@@ -241,6 +287,8 @@ def run_ours(args, rank, world, local_rank):
         launches0 = tr.launch_count()
         if profile_gemm:
             lib.profile_gemm_begin(ctx)
+            if world > 1:
+                lib.dp_timing_begin(ctx)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         last = 0.0
@@ -256,7 +304,10 @@ def run_ours(args, rank, world, local_rank):
 
             n, tms, fl = ctypes.c_int64(), ctypes.c_double(), ctypes.c_double()
             lib.profile_gemm_end(ctx, ctypes.byref(n), ctypes.byref(tms), ctypes.byref(fl))
-            prof = (n.value, tms.value, fl.value)
+            waits, exposed = ctypes.c_int64(), ctypes.c_double()
+            if world > 1:
+                lib.dp_timing_end(ctx, ctypes.byref(waits), ctypes.byref(exposed))
+            prof = (n.value, tms.value, fl.value, waits.value, exposed.value)
         if dist is not None:
             t = torch.tensor([ms], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -274,62 +325,102 @@ def run_ours(args, rank, world, local_rank):
     tokens_per_step = B * T * accum * world
     value = tokens_per_step * K / (ms_dev / 1e3)
     e2e = tokens_per_step * K / (ms_e2e / 1e3)
-    n_gemm, gemm_ms, gemm_flops = prof
+    n_gemm, gemm_ms, gemm_flops, dp_waits, dp_exposed_ms = prof
     achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
     fpt = flops_per_token(V, T, C, L, F)
     hwm = tr.high_water_bytes()
     nparams = tr.num_params()
     nbuckets = tr.num_buckets()
+    dp = None
+    if world > 1:
+        # every rank must hold the same weights after the same reduced gradients: a digest of all parameters, gathered from every rank
+        import hashlib
+
+        hsh = hashlib.blake2b(digest_size=16)
+        params = tr.get("param")
+        for name in sorted(params):
+            hsh.update(params[name].tobytes())
+        mine = torch.frombuffer(bytearray(hsh.digest()), dtype=torch.uint8).cuda()
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        t = torch.tensor([dp_exposed_ms, gemm_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dp = {"dp_weights_identical": bool(all(torch.equal(e, every[0]) for e in every)), "weights_digest_rank0": bytes(every[0].cpu().numpy()).hex(),
+              "exposed_comm_ms_per_step": float(t[0]) / K, "gemm_ms_per_step_with_comm_in_flight": float(t[1]) / K,
+              "note": "exposed = time the compute stream waits for the last reduced bucket after backward has been queued (events on both streams, max over ranks); "
+                      "compare gemm_ms_per_step with the 1-GPU line's roofline.kernel figure for the slowdown of the GEMMs while NCCL runs beside them",
+              "nccl_max_ctas": os.environ.get("NCCL_MAX_CTAS")}
     tr.close()
 
-    cpu = None
+    cpu = kernels = ref_cuda = None
+    if rank == 0 and world == 1 and not args.no_kernels:
+        torch.cuda.synchronize()
+        lib.arena_release_cached(ctx)  # the trainer's arena (tens of GB) goes back to the driver before the microbenchmarks allocate
+        kernels = kernel_suite(5, 3, local_rank)
+    if rank == 0 and world == 1 and not args.no_reference_cuda:
+        torch.cuda.synchronize()
+        lib.arena_release_cached(ctx)
+        torch.cuda.empty_cache()
+        ref_cuda = reference_cuda_run(args.workload, 3, 1)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        tok_s, cores, desc, kind = reference_cpu_run(args.workload, 1, 1)
+        tok_s, cores, desc, kind, _ = reference_cpu_run(args.workload, 3, 1)
         cpu = {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": desc}
     if rank == 0:
         line = {
             "metric": "GPT fp32 train tokens/s (fwd+bwd+AdamW)", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_dev / K,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic: Zipf(1.1) tokens (seed 1000+rank), N(0,0.02) weights (seed 0)",
             "config": {"workload": args.workload, "arch": arch, "layers": L, "d_model": C, "heads": H, "d_ff": F, "seq_len": T, "vocab": V, "batch_per_gpu": B, "micro_batches_per_step": accum,
-                       "global_batch": B * accum * world, "params": nparams, "parallelism": "dp%d" % world, "gradient_buckets": nbuckets,
+                       "global_batch": B * accum * world, "params": nparams, "clip": CLIP, "parallelism": "dp%d" % world, "gradient_buckets": nbuckets,
                        "l2": "working set per step (%.1f GB arena high-water) far exceeds the 126 MB L2" % (hwm / 1e9), "gemm_engine": {1: "simt_fp32", 2: "tcgen05_split_fp32(mode %d)" % split_mode}.get(engine, "none"),
                        "algorithmic_gflop_per_token": fpt / 1e9, "step_tflops": fpt * tokens_per_step / world / (ms_dev / K / 1e3) / 1e12},
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8 * accum, "d2h_bytes_per_step": 4 * accum, "ms_per_step": ms_e2e / K, "last_loss": last_loss},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tensor_tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tensor_tflops"],
-                         "traffic": 232.7e6, "traffic_note": "dram read+write of one captured launch of the most frequent shape (M=32768, N=K=1024; algorithmic 272.6 MB, part of C still in L2): profiles/gemm_tc_pair_kernel_linear_fwd_32768x1024x1024.md",
+                         "traffic": profile_traffic(TRAFFIC_PROFILE), "traffic_note": "dram read+write of one captured launch of the most frequent shape (M=32768, N=K=1024; algorithmic 272.6 MB), read from profiles/" + TRAFFIC_PROFILE,
                          "frac_of_split_ceiling": achieved / (pk["tensor_tflops"] / units),
                          "kernel": "gemm (%d launches, %.1f ms of the timed region)" % (n_gemm, gemm_ms),
                          "peak_source": "%s dense bf16, sustained; split mode %d spends the tensor time of %d bf16 MMAs per product (a tf32 MMA counts 2), so its ceiling is 1/%d of this" % (pk["source"], split_mode, units, units),
                          "gemm_share_of_step": gemm_ms / ms_dev},
             "cpu_baseline": cpu,
         }
+        if kernels is not None:
+            # the second half of the metric: every bandwidth-bound backward / optimizer kernel against the measured HBM peak
+            line["kernels"] = kernels
+            line["bwd_kernel_frac_of_hbm_peak"] = {k: round(v["frac_of_hbm_peak"], 4) for k, v in kernels.items()}
+            line["peak_hbm_gbs"] = pk["hbm_gbs"]
+        if ref_cuda is not None:
+            line["reference_cuda"] = ref_cuda
+            line["vs_reference_cuda"] = (value / ref_cuda["value"]) if "value" in ref_cuda else None
+        if dp is not None:
+            line["dp"] = dp
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 
 
 # ---- fused backward kernels vs the HBM roofline -----------------------------------------------------------------------
-def run_kernels(args):
+def kernel_suite(steps, warmup, device=0):
+    """The bandwidth-bound kernels of the backward pass and the optimizer at the microbenchmark shapes, each timed alone with
+    CUDA events (L2 flushed by a 256 MB write before every sample): {name: {ms, algorithmic_bytes, achieved_gbs,
+    frac_of_hbm_peak}}.  Algorithmic bytes count every operand once."""
     import numpy as np
     import torch
 
-    from gradcraft_b200 import capi
+    from gradcraft_b200 import capi, synth
 
-    ctx = capi.Context(0)
+    ctx = capi.Context(device)
     pk = peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
     def timeit(fn, calls=1):
         """Median ms per call.  calls > 1: that many back-to-back launches per sample, fn(i) working on the i-th of `calls`
-        disjoint buffer sets (so no launch finds its data in L2); for kernels of a few tens of microseconds, whose
-        single-launch event timing is mostly queueing latency rather than the kernel."""
-        for _ in range(max(3, args.warmup)):
+        disjoint buffer sets (so no launch finds its data in L2)."""
+        for _ in range(max(3, warmup)):
             for i in range(calls):
                 fn(i)
         ts = []
-        for _ in range(max(5, args.steps)):
+        for _ in range(max(5, steps)):
             flush.zero_()  # evict L2 between timed samples
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
@@ -340,13 +431,12 @@ def run_kernels(args):
             ts.append(s.elapsed_time(e) / calls)
         return float(np.median(ts))
 
-    out = {}
+    out, notes = {}, {}
     M, V = 16384, 32768
     P = torch.rand(M, V, device="cuda")
     P /= P.sum(-1, keepdim=True)
     Tg = torch.randint(0, V, (M,), dtype=torch.int32, device="cuda")
-    ms = timeit(lambda i: ctx.softmax_ce_bwd_f32(P, P, Tg, capi.IDX_I32, 1.0, M, V, 0))
-    out["softmax_ce_bwd [16384,32768]"] = (ms, 2 * M * V * 4 + M * 4)
+    out["softmax_ce_bwd [16384,32768]"] = (timeit(lambda i: ctx.softmax_ce_bwd_f32(P, P, Tg, capi.IDX_I32, 1.0, M, V, 0)), 2 * M * V * 4 + M * 4)
     del P
     M, C = 16384, 1024
     g, b, dg, db = torch.ones(C, device="cuda"), torch.zeros(C, device="cuda"), torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
@@ -358,31 +448,60 @@ def run_kernels(args):
         sets.append((x, dy, dx, mu, rs))
         del y
     ln = lambda i: ctx.layernorm_bwd_f32(sets[i][2], dg, db, sets[i][1], sets[i][0], g, sets[i][3], sets[i][4], M, C, 0, 0)
-    ms = timeit(ln, calls=4)
-    ms_single = timeit(ln)
-    out["layernorm_bwd [16384,1024]"] = (ms, 3 * M * C * 4 + 2 * M * 4 + 3 * C * 4)
+    ln_bytes = 3 * M * C * 4 + 2 * M * 4 + 3 * C * 4
+    out["layernorm_bwd [16384,1024]"] = (timeit(ln), ln_bytes)  # one isolated call per sample: the headline
+    out["layernorm_bwd [16384,1024] pipelined x4"] = (timeit(ln, calls=4), ln_bytes)
+    notes["layernorm_bwd [16384,1024] pipelined x4"] = "four back-to-back calls on four disjoint buffer sets per sample: launch latency hidden, as inside a training step"
+    rms = lambda i: ctx.rmsnorm_bwd_f32(sets[i][2], dg, sets[i][1], sets[i][0], g, sets[i][4], M, C, 0, 0)
+    out["rmsnorm_bwd [16384,1024]"] = (timeit(rms), 3 * M * C * 4 + M * 4 + 2 * C * 4)
     del sets
     M, F = 16384, 4096
     x, dy = torch.randn(M, F, device="cuda"), torch.randn(M, F, device="cuda") * 1e-2
     dx = torch.empty_like(x)
-    ms = timeit(lambda i: ctx.gelu_bwd_f32(dx, dy, x, M * F, 0))
-    out["gelu_bwd [16384,4096]"] = (ms, 3 * M * F * 4)
+    out["gelu_bwd [16384,4096]"] = (timeit(lambda i: ctx.gelu_bwd_f32(dx, dy, x, M * F, 0)), 3 * M * F * 4)
+    red = torch.empty(F, device="cuda")
+    out["reduce_rows (bias gradient) [16384,4096]"] = (timeit(lambda i: ctx.reduce_rows_f32(red, dy, M, F, 0)), M * F * 4 + F * 4)
     del x, dy, dx
     Bn, H, T = 16, 16, 1024
     rows = Bn * H * T
     S = torch.randn(rows, T, device="cuda")
-    ctx.causal_softmax_fwd_f32(S, S, 0.125, rows, T)
+    tri = 4 * Bn * H * T * ((T + 1) // 2)  # bytes of one pass over the entries at or below the diagonal
+    out["causal_softmax_fwd [16,16,1024,1024]"] = (timeit(lambda i: ctx.causal_softmax_fwd_f32(S, S, 0.125, rows, T)), tri + 4 * rows * T)
     dP = torch.randn(rows, T, device="cuda") * 1e-2
-    ms = timeit(lambda i: ctx.causal_softmax_bwd_f32(dP, dP, S, 0.125, rows, T, 0))
-    out["causal_softmax_bwd [16,16,1024,1024]"] = (ms, 4 * Bn * H * T * (2 * (T + 1) // 2 + T))
+    out["causal_softmax_bwd [16,16,1024,1024]"] = (timeit(lambda i: ctx.causal_softmax_bwd_f32(dP, dP, S, 0.125, rows, T, 0)), 2 * tri + 4 * rows * T)
+    del S, dP
+    n, Vv, Wd = 32768, 32768, 1024
+    idx_h = synth.zipf_tokens(4321, n, Vv).astype(np.int64)
+    idx = torch.from_numpy(idx_h).cuda()
+    dyv, table = torch.randn(n, Wd, device="cuda") * 1e-2, torch.zeros(Vv, Wd, device="cuda")
+    hit = int(np.unique(idx_h).size)
+    out["scatter_add [32768 Zipf(1.1) tokens, 32768 x 1024 table]"] = (timeit(lambda i: ctx.scatter_add_f32(table, idx, capi.IDX_I64, dyv, n, Wd, Vv)), n * Wd * 4 + 2 * hit * Wd * 4)
+    notes["scatter_add [32768 Zipf(1.1) tokens, 32768 x 1024 table]"] = "%d distinct rows hit; bytes = dy once + read-modify-write of the rows hit" % hit
+    del dyv, table
+    npar = 185759744
+    npar_pad = (npar + capi.ADAMW_CHUNK - 1) // capi.ADAMW_CHUNK * capi.ADAMW_CHUNK
+    w, m, v, gr = (torch.randn(npar_pad, device="cuda") * 0.02 for _ in range(4))
+    v.abs_()
+    mask = torch.ones(npar_pad // capi.ADAMW_CHUNK, dtype=torch.uint8, device="cuda")
+    out["adamw_arena [185.8 M parameters]"] = (timeit(lambda i: ctx.adamw_arena_f32(w, m, v, gr, mask, npar_pad, 3e-4, 0.9, 0.95, 0.9, 0.95, 0.1, 1e-5, 1.0)), 28 * npar_pad)
+    del w, m, v, gr
     ctx.sync()
     kernels = {k: {"ms": ms, "algorithmic_bytes": by, "achieved_gbs": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / pk["hbm_gbs"]} for k, (ms, by) in out.items()}
-    kernels["layernorm_bwd [16384,1024]"]["timing"] = "4 back-to-back launches on 4 disjoint buffer sets per sample; one isolated launch per sample reads %.4f ms (two launches of ~35 us and ~3 us: queueing latency dominates)" % ms_single
+    for k, t in notes.items():
+        kernels[k]["note"] = t
+    ctx.close()
+    del flush
+    torch.cuda.empty_cache()
+    return kernels
+
+
+def run_kernels(args):
+    pk = peaks()
+    kernels = kernel_suite(args.steps, args.warmup)
     worst = min(kernels.values(), key=lambda d: d["frac_of_hbm_peak"])
     print(json.dumps({"metric": "fused backward kernels, achieved HBM GB/s vs measured peak", "value": worst["frac_of_hbm_peak"], "unit": "fraction of HBM peak (worst kernel)", "n_gpus": 1,
                       "steps": max(5, args.steps), "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "f32", "data": "synthetic N(0,1) activations, N(0,1e-2) upstream gradients",
                       "config": {"workload": "kernels", "l2": "flushed between timed launches (256 MB write)"}, "peak_hbm_gbs": pk["hbm_gbs"], "peak_source": pk["source"], "kernels": kernels}))
-    ctx.close()
 
 
 # ---- the GEMM shapes of one gpt180m step vs the tensor roofline -------------------------------------------------------------
@@ -456,6 +575,8 @@ def main():
     ap.add_argument("--ref-batch", type=int, default=0, help="sequences per step for --impl reference-cuda (default: the workload's)")
     ap.add_argument("--workload", default="gpt180m", choices=list(WORKLOADS) + ["kernels", "gemm"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the fused-kernel microbenchmarks of the default line")
+    ap.add_argument("--no-reference-cuda", action="store_true", help="skip the reference-CUDA leg of the default line")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
     ap.add_argument("--only", default="", help="gemm workload: run only the shapes whose name contains this text")
     args = ap.parse_args()

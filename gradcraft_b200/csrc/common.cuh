@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -71,6 +72,11 @@ struct gcb_ctx {
     int* d_status = nullptr;   // device-side status word written by kernels that give up on a bounded wait
     void* nccl_comm = nullptr;
     int dp_rank = 0, dp_world = 1;
+    std::atomic<int> dp_failed{0};   // 0, or the status (GCB_NCCL_ERROR / GCB_TIMEOUT) the communicator watchdog ended with
+    void* dp_watchdog = nullptr;     // host thread watching the communicator (dp.cu)
+    bool dp_timing = false;          // optional timing of how long the compute stream waits for the reductions
+    std::vector<cudaEvent_t> dp_events;
+    size_t dp_used = 0;
     void* tma_encode = nullptr;  // cuTensorMapEncodeTiled, resolved lazily
     // optional timing of every GEMM launch with CUDA events on the compute stream
     bool prof_on = false;

@@ -254,6 +254,11 @@ int gcb_selftest_bounded_wait(gcb_ctx* ctx, int max_polls) {
 // Reads the device status word after the stream has been synchronised: a kernel that gave up on a bounded wait, or an
 // index / target that was skipped because it lay outside its table, turns into an error of the call that blocked.
 static int check_status_word(gcb_ctx* ctx) {
+    if (const int f = ctx->dp_failed.load()) {
+        set_error(f == GCB_TIMEOUT ? "data parallel: a gradient all-reduce did not complete in time; the communicator was aborted and the gradients of this step are invalid"
+                                   : "data parallel: NCCL reported an asynchronous error; the communicator was aborted and the gradients of this step are invalid");
+        return f;
+    }
     int st[4];
     GCB_CHECK_CUDA(cudaMemcpy(st, ctx->d_status, sizeof(st), cudaMemcpyDeviceToHost));
     if (st[0] != 0) {

@@ -282,6 +282,24 @@ GCB_API int gcb_dp_init(gcb_ctx* ctx, const uint8_t id[GCB_DP_ID_BYTES], int ran
 GCB_API int gcb_dp_allreduce_avg_f32(gcb_ctx* ctx, float* buf, int64_t n);
 GCB_API int gcb_dp_wait(gcb_ctx* ctx);
 GCB_API int gcb_dp_finalize(gcb_ctx* ctx);
+/* Failure handling (host side).  gcb_dp_init gives up with GCB_TIMEOUT when the communicator is not up after
+ * GRADC_DP_INIT_TIMEOUT_S seconds (default 180: a rank never joined, or the id is not rank 0's).  Afterwards a host thread
+ * polls ncclCommGetAsyncError and the completion of the reductions queued before the last gcb_dp_wait; on an error, or when
+ * those take longer than GRADC_DP_TIMEOUT_S seconds (default 300, 0 = never), it calls ncclCommAbort and the context is
+ * marked failed: gcb_dp_allreduce_avg_f32, gcb_dp_wait, gcb_ctx_sync and gcb_copy_d2h return GCB_NCCL_ERROR / GCB_TIMEOUT
+ * from then on, and gcb_dp_finalize releases what is left.
+ * gcb_dp_selftest runs that machinery against host-side stand-ins for the NCCL calls (no GPU needed): scenario 0 healthy,
+ * 1 a reduction that never completes, 2 an asynchronous error, 3 a communicator creation that never returns, 4 one that fails;
+ * it returns the status the caller of the real entry points would see and how often abort was called.
+ * gcb_dp_selftest_rendezvous is the same host timeout around a rendezvous through a directory (each rank drops a file and
+ * waits for all `world` files), for multi-process tests of "a rank never joins" and "wrong id" without a GPU. */
+GCB_API int gcb_dp_selftest(int scenario, int timeout_ms, int* abort_calls);
+GCB_API int gcb_dp_selftest_rendezvous(const char* dir, int rank, int world, int timeout_ms);
+/* Measurement aid: between begin and end every gcb_dp_wait records one event on the compute stream (backward has been
+ * queued) and one on the communication stream (the last bucket is reduced); end synchronises and returns the number of waits
+ * and the summed time by which the second follows the first, i.e. how long the compute stream sat waiting for NCCL. */
+GCB_API int gcb_dp_timing_begin(gcb_ctx* ctx);
+GCB_API int gcb_dp_timing_end(gcb_ctx* ctx, int64_t* waits, double* exposed_ms);
 
 #ifdef __cplusplus
 }

@@ -31,6 +31,7 @@
 
 #include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <iostream>
@@ -165,6 +166,10 @@ static int run_gpt(Model& model, int64_t V, int64_t T, int64_t B, int64_t steps,
     std::ofstream lossf(prefix + "_loss.txt");
     lossf.precision(9);
     std::ofstream timef(prefix + "_time.txt");
+    // Timing runs (bench.py): REF_HARNESS_NO_DUMP=1 skips the gradient / weight dumps, which would otherwise sit inside the
+    // timed step; REF_HARNESS_SAMPLE_T=<t> feeds sequences of t <= T tokens (a bounded sample of the same model).
+    const bool dump = std::getenv("REF_HARNESS_NO_DUMP") == nullptr;
+    if (const char* st = std::getenv("REF_HARNESS_SAMPLE_T")) { const int64_t t = std::stoll(st); if (t >= 1 && t <= T) T = t; }
 
     for (int64_t step = 1; step <= steps; ++step) {
         auto t0 = std::chrono::high_resolution_clock::now();
@@ -185,7 +190,7 @@ static int run_gpt(Model& model, int64_t V, int64_t T, int64_t B, int64_t steps,
             scaled.backward();
         }
         float norm = -1.0f;
-        if (step == 1 || step == steps) {
+        if (dump && (step == 1 || step == steps)) {
             Dict g;
             for (auto& [name, p] : model.named_parameters()) {
                 if (p->grad().has_value()) g[name] = dense_copy(p->grad().value());
@@ -197,7 +202,7 @@ static int run_gpt(Model& model, int64_t V, int64_t T, int64_t B, int64_t steps,
         auto t1 = std::chrono::high_resolution_clock::now();
         lossf << step_loss << " " << norm << "\n";
         timef << std::chrono::duration<double, std::milli>(t1 - t0).count() << "\n";
-        if (step == 1 || step == steps) save_tensor_checkpoint(model.state_dict(cpu), prefix + "_weights" + std::to_string(step) + ".ckpt");
+        if (dump && (step == 1 || step == steps)) save_tensor_checkpoint(model.state_dict(cpu), prefix + "_weights" + std::to_string(step) + ".ckpt");
     }
     return 0;
 }

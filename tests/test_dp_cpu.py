@@ -103,3 +103,72 @@ def test_two_ranks_bucketed_average_equals_whole_average_gloo():
         assert p.exitcode == 0
     assert all(ok for _, ok, _ in out)
     assert out[0][2] == out[1][2]  # both ranks hold identical reduced gradients
+
+
+# ---- failure path of the gradient exchange, host side only (no GPU is made to fail) ------------------------------------------
+def _lib():
+    import __graft_entry__ as entry
+
+    entry.build()
+    from gradcraft_b200 import capi
+
+    return capi, capi.lib()
+
+
+@pytest.mark.parametrize("scenario,status,aborts", [(0, "OK", 0), (1, "TIMEOUT", 1), (2, "NCCL_ERROR", 1), (3, "TIMEOUT", 0), (4, "NCCL_ERROR", 0)])
+def test_communicator_watchdog_and_guarded_creation(scenario, status, aborts):
+    """The watchdog and the creation timeout that guard the NCCL communicator, driven by stand-ins for the NCCL calls: a
+    healthy reduction, one that never completes, an asynchronous error, a creation that never returns (a peer never joined)
+    and one that fails (bad unique id).  Failures end in a status code and one ncclCommAbort, never in a wait without end."""
+    capi, lib = _lib()
+    n = ctypes.c_int(-1)
+    if status == "OK":
+        assert lib.dp_selftest(scenario, 150, ctypes.byref(n)) == capi.OK
+    else:
+        with pytest.raises(capi.GcbError) as e:
+            lib.dp_selftest(scenario, 150, ctypes.byref(n))
+        assert e.value.status == getattr(capi, status)
+    assert n.value == aborts
+
+
+def _rendezvous_rank(rank, world, port, directory, joins, q):
+    import torch.distributed as dist
+
+    sys.path.insert(0, ROOT)
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    capi, lib = _lib()
+    status = "skipped"
+    if joins:
+        try:
+            lib.dp_selftest_rendezvous(directory.encode(), rank, world, 1500)
+            status = "OK"
+        except capi.GcbError as e:
+            status = {capi.TIMEOUT: "TIMEOUT", capi.NCCL_ERROR: "NCCL_ERROR"}.get(e.status, str(e.status))
+    # the survivors learn on the host who made it (a store / heartbeat in a real job) before anything is queued on a device
+    seen = [None] * world
+    dist.all_gather_object(seen, status)
+    q.put((rank, status, seen))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["all_join", "one_never_joins", "wrong_id"])
+def test_two_ranks_rendezvous_under_the_creation_timeout_gloo(case, tmp_path):
+    """Two CPU ranks (gloo for the out-of-band channel) go through the guarded communicator creation with a directory
+    rendezvous standing in for ncclCommInitRank: both join -> OK; rank 1 never calls it -> rank 0 gets GCB_TIMEOUT instead of
+    waiting for ever, before any collective exists; a directory that does not exist (wrong id) -> GCB_NCCL_ERROR at once."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + (os.getpid() % 90) + {"all_join": 0, "one_never_joins": 100, "wrong_id": 200}[case]
+    directory = str(tmp_path / ("absent" if case == "wrong_id" else ""))
+    procs = [ctx.Process(target=_rendezvous_rank, args=(r, 2, port, directory, not (case == "one_never_joins" and r == 1), q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    want = {"all_join": ["OK", "OK"], "one_never_joins": ["TIMEOUT", "skipped"], "wrong_id": ["NCCL_ERROR", "NCCL_ERROR"]}[case]
+    assert [s for _, s, _ in out] == want
+    assert all(seen == want for _, _, seen in out)  # every rank knows the outcome of every other
