@@ -116,7 +116,8 @@ class ClockSampler:
 
 
 # ---- reference CPU arm -------------------------------------------------------------------------------------
-CPU_SAMPLE_T = 256  # tokens per CPU step: one sequence cut to 256 tokens (~4 s of host work per step for gpt180m on 16 cores)
+CPU_SAMPLE_T = None  # tokens per CPU step: None = one full sequence (~16 s of host work per step for gpt180m on 16 cores; shorter samples would
+                     # overweight the optimizer pass over all parameters, whose cost does not depend on the number of tokens)
 
 
 def reference_cpu_run(workload, steps, warmup, sample_B=1, sample_T=None):
@@ -124,7 +125,7 @@ def reference_cpu_run(workload, steps, warmup, sample_B=1, sample_T=None):
     bounded sample: the workload's model with its seeded weights, sample_B sequences of sample_T tokens per step.
     Returns (tokens/s, cores, description, kind, ms per timed step)."""
     arch, V, T, C, H, L, F, B, accum = WORKLOADS[workload]
-    sample_T = min(T, sample_T or CPU_SAMPLE_T)
+    sample_T = min(T, sample_T or CPU_SAMPLE_T or T)
     harness = os.path.join(ROOT, "oracle", "_ref", "ref_harness")
     cores = os.cpu_count() or 1
     if not os.path.exists(harness):
@@ -195,14 +196,16 @@ def run_reference_cuda_arm(args, rank):
 
 
 def run_reference_arm(args, rank):
-    """The reference's CPU implementation on the host cores: exactly --warmup untimed and --steps timed steps, each a bounded
-    sample (one sequence cut to CPU_SAMPLE_T tokens); more steps than fit in about four minutes are cut and the line says so."""
+    """The reference's CPU implementation on the host cores: --warmup untimed and --steps timed steps, each a bounded sample (one
+    sequence instead of the GPU arm's 32); steps beyond what fits in about four minutes are cut, and the line reports the counts
+    and the per-step time that were actually run (the requested ones go to steps_requested / warmup_requested)."""
     if rank != 0:
         return
     arch, V, T, C, H, L, F, B, accum = WORKLOADS[args.workload]
     t0 = time.time()
-    est_s = 4.5 * (flops_per_token(V, min(T, CPU_SAMPLE_T), C, L, F) * min(T, CPU_SAMPLE_T)) / (flops_per_token(32768, 256, 1024, 12, 4096) * 256)  # ~4.5 s per step for gpt180m on 16 cores
-    fit = max(1, int(240.0 / max(est_s, 1e-3)))
+    Ts = min(T, CPU_SAMPLE_T or T)
+    est_s = 16.0 * (flops_per_token(V, Ts, C, L, F) * Ts) / (flops_per_token(32768, 1024, 1024, 12, 4096) * 1024)  # ~16 s per full-sequence step for gpt180m on 16 cores
+    fit = max(2, int(240.0 / max(est_s, 1e-3)))
     warm = min(args.warmup, max(1, fit // 5))
     steps = max(1, min(args.steps, fit - warm))
     tok_s, cores, desc, kind, ms_step = reference_cpu_run(args.workload, steps, warm)
@@ -363,7 +366,7 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.empty_cache()
         ref_cuda = reference_cuda_run(args.workload, 3, 1)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        tok_s, cores, desc, kind, _ = reference_cpu_run(args.workload, 3, 1)
+        tok_s, cores, desc, kind, _ = reference_cpu_run(args.workload, 1, 1)
         cpu = {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": desc}
     if rank == 0:
         line = {

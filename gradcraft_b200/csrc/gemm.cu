@@ -19,6 +19,16 @@ static int dispatch_gemm(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g, cons
         if (rc == GCB_OK && g.gelu_act) rc = gcb_gelu_fwd_f32(ctx, g.gelu_act, g.C, g.M * g.N);
         return rc;
     }
+    if (rc == GCB_UNSUPPORTED && g.colsum) {
+        // no kernel gathers the column sums of op(B) for this problem: the same product, then the row reduction as a pass of its own
+        GemmArgs plain = g;
+        plain.colsum = nullptr;
+        rc = dispatch_gemm(ctx, ta, tb, plain, who);
+        if (rc != GCB_OK) return rc;
+        if (!tb) return gcb_reduce_rows_f32(ctx, g.colsum, g.B, g.K, g.N, g.colsum_accumulate);
+        set_error("%s: column sums need op(B) stored K x N with ldb == N", who);
+        return GCB_UNSUPPORTED;
+    }
     if (rc == GCB_UNSUPPORTED) {
         if (ctx->gemm_engine == 2) {
             set_error("%s: the tcgen05 engine was forced but cannot take these operands (alignment / leading dimensions)", who);
@@ -63,6 +73,18 @@ int gcb_gemm_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t
     GCB_REQUIRE(ctx, "gcb_gemm_f32: ctx is NULL");
     GemmArgs g{M, N, K, alpha, beta, A, B, bias, C, lda, ldb, ldc, 0, 0, 0, 0, 0, 0, 1, 1};
     return run_gemm(ctx, op_a, op_b, g, "gcb_gemm_f32");
+}
+
+int gcb_gemm_colsum_f32(gcb_ctx* ctx, int op_a, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda, const float* B, float beta, float* C, int64_t ldc, float* colsum,
+                        int colsum_accumulate) {
+    GCB_REQUIRE(ctx, "gcb_gemm_colsum_f32: ctx is NULL");
+    GCB_REQUIRE(N == 0 || colsum, "gcb_gemm_colsum_f32: colsum is NULL");
+    if (K == 0 && N > 0 && !colsum_accumulate) { int rc = gcb_fill_f32(ctx, colsum, 0.0f, N); if (rc) return rc; }
+    GemmArgs g{M, N, K, alpha, beta, A, B, nullptr, C, lda, N, ldc, 0, 0, 0, 0, 0, 0, 1, 1};
+    g.colsum = colsum;
+    g.colsum_accumulate = colsum_accumulate;
+    if (M == 0 && N > 0 && K > 0) return gcb_reduce_rows_f32(ctx, colsum, B, K, N, colsum_accumulate);  // no product, but the sums are still owed
+    return run_gemm(ctx, op_a, GCB_OP_N, g, "gcb_gemm_colsum_f32");
 }
 
 int gcb_gemm_batched_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda, int64_t a_so, int64_t a_si, const float* B,

@@ -22,6 +22,10 @@ struct GemmArgs {
     const float* sm_probs = nullptr;
     const float* sm_rowdot = nullptr;
     float sm_scale = 1.0f;
+    // column sums of op(B) as a by-product (the bias gradient next to dW = X^T dY: op(B) = dY): colsum[n] = sum_k op(B)[k, n]
+    // (+ colsum[n] when colsum_accumulate).  Unbatched problems only.
+    float* colsum = nullptr;
+    int colsum_accumulate = 0;
 };
 
 // fp32 FMA engine: any shape, any leading dimension.

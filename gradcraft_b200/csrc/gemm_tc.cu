@@ -53,12 +53,19 @@ struct TcParams {
                          // 1: three TF32 products; big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
                          // 0: as 1 with big = rna_tf32(x) written back, small = x - big (does not rely on the hardware's truncation)
     float* partial;      // [splits][M][N] when splits > 1
+    int c_tma;               // 256-wide single-CTA kernel: C leaves (and the probabilities arrive) through TMA on swizzled 32 x 32 blocks in shared memory
+    float* colsum;           // column sums of op(B) (see GemmArgs), or NULL: pair kernel with B stored K x N only
+    float* colsum_partial;   // [splits][N] when splits > 1
+    int colsum_accumulate;
     const float* gelu_pre;   // GELU-backward epilogue (see GemmArgs), or NULL: applied by the pair kernel only
     float* gelu_act;         // GELU-forward second output (see GemmArgs), or NULL: pair kernel only
     const float* sm_probs;   // softmax-backward epilogue (see GemmArgs), or NULL
     const float* sm_rowdot;
     float sm_scale;
     int* status;
+#ifdef GCB_TC_TRACE
+    int dbg;  // timing experiments (results are wrong): 1 B is not split, 2 A is not moved to tensor memory, 4 the epilogue stores nothing
+#endif
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -90,6 +97,13 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
                  "r"(c4)
                  : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }  // the sources of all but the last N groups have been read
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
     uint64_t d = 0;
     d |= (uint64_t)((addr >> 4) & 0x3FFF);
@@ -188,7 +202,7 @@ __device__ __forceinline__ void split_a_to_tmem(const uint8_t* raw, uint32_t tad
 // 128 B apart along K (LBO), 256 B apart along M / N (SBO) — whatever the raw tile's orientation.
 // ROWS = rows of the operand tile (its M or N extent).  t = thread index among the 128 splitter threads.
 template <bool MN, int ROWS>
-__device__ __forceinline__ void split_hybrid(const uint8_t* raw, uint8_t* twin, int t) {
+__device__ __forceinline__ void split_hybrid(const uint8_t* raw, uint8_t* twin, int t, float* colsum = nullptr) {
     uint8_t* big = twin;
     uint8_t* sml = twin + ROWS * 32;
     if (!MN) {
@@ -213,6 +227,8 @@ __device__ __forceinline__ void split_hybrid(const uint8_t* raw, uint8_t* twin, 
             float x[16];
 #pragma unroll
             for (int k = 0; k < 16; ++k) x[k] = *reinterpret_cast<const float*>(box + k * 128 + ((((j >> 3) ^ (k & 3)) << 5) | ((j & 7) << 2)));
+            if (colsum != nullptr)  // this thread's column over the 16 rows of the K block, pairwise, then onto the running sum (fixed order: deterministic)
+                *colsum += (((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]))) + (((x[8] + x[9]) + (x[10] + x[11])) + ((x[12] + x[13]) + (x[14] + x[15])));
             const uint32_t off = (uint32_t)(mn >> 3) * 256u + (uint32_t)(mn & 7) * 16u;
 #pragma unroll
             for (int kc = 0; kc < 2; ++kc) {
@@ -274,9 +290,12 @@ struct TcSmem {
     static constexpr int A_TMEM_COL0 = 2 * BN;
     static_assert(!A_TM || (BN <= 128 && A_TMEM_COL0 + STAGES * 32 <= TMEM_COLS), "A stages do not fit beside the accumulators");
     static constexpr int EPI_PITCH = 36;                           // floats per staged row: 32 + 4 keeps float4 alignment and spreads banks
-    static constexpr int EPI_BYTES = EPI_WARPS * 32 * EPI_PITCH * 4;  // one 32 x 32 transposition buffer per epilogue warp
+    // one 32 x 32 transposition buffer per epilogue warp; the 256-wide kernel instead keeps two 4 KB blocks per warp in the
+    // 128-byte-swizzled layout its TMA stores (and probability loads) use
+    static constexpr int EPI_BYTES = BN == 256 ? EPI_WARPS * 2 * 4096 : EPI_WARPS * 32 * EPI_PITCH * 4;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int TOTAL = BAR_OFFSET + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    static_assert((STAGES * STAGE_BYTES) % 1024 == 0, "epilogue blocks must sit on the swizzle pattern's 1 KB boundary");
 };
 
 struct TileCoord {
@@ -344,7 +363,8 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int64_t w, in
 // epilogue warps drain tile i while the issuer already accumulates tile i + 1.
 // A_MN: A is stored K x M (contiguous along M); B_MN: B is stored K x N (contiguous along N).
 template <int BN, bool A_MN, bool B_MN, bool A_TM>
-__global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+__global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                                                                 const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_p, TcParams p) {
     using S = TcSmem<BN, A_TM>;
     constexpr int TC_STAGES = S::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -358,12 +378,14 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
     auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * TC_STAGES + 2 + b); };
     const uint32_t tmem_slot = bars + 8u * (3 * TC_STAGES + 4);
     volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen_base + S::BAR_OFFSET + 8 * (3 * TC_STAGES + 4));
+    auto probs_bar = [&](int ew, int b) { return bars + 8u * (3 * TC_STAGES + 5 + 2 * ew + b); };  // 256-wide kernel: a probability block has landed in (warp, buffer)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(conv_bar(s), 4); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), S::EPI_WARPS); }
+        if (BN == 256) for (int e = 0; e < 2 * S::EPI_WARPS; ++e) mbar_init(probs_bar(e >> 1, e & 1), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {  // TMEM allocation is warp-wide
@@ -532,6 +554,98 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
     } else {
         // ---------------- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. +31, i.e. 32 rows of the tile ----------------
         const int q = warp & 3, ew = warp - 6;
+        bool tma_path = false;
+        if constexpr (BN == 256) tma_path = p.c_tma != 0;
+        if (tma_path) {
+            // ---- 256-wide tiles with short K loops (attention scores / dS) are bound by this epilogue: the warp only moves its
+            // 32 x 32 block from tensor memory into a swizzled 4 KB block of shared memory (applying the epilogue arithmetic on
+            // the way) and one lane hands the block to the TMA unit, which writes whole lines to global memory while the warp
+            // is already on its next block.  For dS the probabilities arrive the same way, into the block dS is then built in.
+            const int c_begin = (ew >> 2) * 4;
+            const uint32_t blk_sh = base + TC_STAGES * S::STAGE_BYTES + ew * 8192;
+            uint8_t* blk_gen = gen_base + TC_STAGES * S::STAGE_BYTES + ew * 8192;
+            const bool has_p = p.sm_probs != nullptr;
+            uint32_t lt = 0, nblk = 0, pcount0 = 0, pcount1 = 0;
+            bool ok = true;
+            TR_BEGIN(3);
+            for (int64_t w = blockIdx.x; w < p.loop_end && ok; w += gridDim.x) {
+                const TileCoord tc = tile_coord(p, w, BN);
+                if (tc.skip) continue;
+                const uint32_t buf = lt & 1u;
+                const int64_t n_end = p.causal == 1 ? min(p.N, (int64_t)tc.m0 + TC_BM) : p.N;
+                const int64_t col0 = (int64_t)tc.n0 + 32 * c_begin;
+                const int nchunks = (int)max((int64_t)0, min((int64_t)4, (n_end - col0 + 31) / 32));
+                const int m_blk = tc.m0 + 32 * q;
+                const int64_t m = (int64_t)m_blk + lane;
+                const float rd = (has_p && m < p.M) ? __ldg(p.sm_rowdot + ((int64_t)tc.b_out * p.batch_inner + tc.b_in) * p.M + m) : 0.0f;
+                if (has_p && nchunks > 0) {  // probabilities of the first block: requested before the accumulator is ready
+                    if (lane == 0) {
+                        tma_store_wait_read<0>();
+                        mbar_expect_tx(probs_bar(ew, nblk & 1), 4096);
+                        tma_load_4d(blk_sh + (nblk & 1) * 4096, &map_p, probs_bar(ew, nblk & 1), (int)col0, m_blk, tc.b_in, tc.b_out);
+                    }
+                }
+                ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int j = 0; j < nchunks; ++j, ++nblk) {
+                    const int c = c_begin + j;
+                    const int64_t nb = (int64_t)tc.n0 + 32 * c;
+                    const uint32_t b = nblk & 1u;
+                    if (lane == 0) {
+                        if (has_p) {
+                            tma_store_wait_read<0>();  // the other block's store has been read out: it can take the next probabilities
+                            if (j + 1 < nchunks) {
+                                mbar_expect_tx(probs_bar(ew, b ^ 1u), 4096);
+                                tma_load_4d(blk_sh + (b ^ 1u) * 4096, &map_p, probs_bar(ew, b ^ 1u), (int)nb + 32, m_blk, tc.b_in, tc.b_out);
+                            }
+                        } else {
+                            tma_store_wait_read<1>();  // this block's previous store (two blocks ago) has been read out
+                        }
+                    }
+                    float v[32];
+                    tmem_ld32(tmem_base + buf * BN + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), v);
+                    if (has_p) {
+                        const uint32_t par = (b ? pcount1 : pcount0) & 1u;
+                        if (b) ++pcount1; else ++pcount0;
+                        ok = __all_sync(0xffffffffu, mbar_wait(probs_bar(ew, b), par, p.status, 6)) != 0;
+                        if (!ok) break;
+                    }
+                    __syncwarp();
+                    uint8_t* row = blk_gen + b * 4096 + lane * 128;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        float4* slot = reinterpret_cast<float4*>(row + ((e ^ (lane & 7)) << 4));  // 128-byte swizzle: 16-byte chunk index XOR (row & 7)
+                        float4 o = make_float4(v[4 * e] * p.alpha, v[4 * e + 1] * p.alpha, v[4 * e + 2] * p.alpha, v[4 * e + 3] * p.alpha);
+                        const int64_t n = nb + 4 * e;
+                        if (p.bias != nullptr) {
+                            o.x += n + 0 < p.N ? __ldg(p.bias + n + 0) : 0.0f; o.y += n + 1 < p.N ? __ldg(p.bias + n + 1) : 0.0f;
+                            o.z += n + 2 < p.N ? __ldg(p.bias + n + 2) : 0.0f; o.w += n + 3 < p.N ? __ldg(p.bias + n + 3) : 0.0f;
+                        }
+                        if (has_p) {  // dS = scale * P * (dP - rowdot), zero above the diagonal
+                            const float4 pr = *slot;
+                            const float sc = p.sm_scale;
+                            o.x = n + 0 <= m ? sc * pr.x * (o.x - rd) : 0.0f; o.y = n + 1 <= m ? sc * pr.y * (o.y - rd) : 0.0f;
+                            o.z = n + 2 <= m ? sc * pr.z * (o.z - rd) : 0.0f; o.w = n + 3 <= m ? sc * pr.w * (o.w - rd) : 0.0f;
+                        }
+                        *slot = o;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the block as written by these threads -> visible to the TMA unit
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_4d(&map_c, blk_sh + b * 4096, (int)nb, m_blk, tc.b_in, tc.b_out);  // rows / columns beyond M / N are clipped by the unit
+                        tma_store_commit();
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                ++lt;
+            }
+            if (lane == 0) tma_store_wait_all();  // nothing of this CTA's shared memory may be in flight when it exits
+            TR_END();
+        } else {
         constexpr int COLS_PER_WARP = BN / 32 / (S::EPI_WARPS / 4);  // 32-column blocks each warp of a lane quarter drains
         const int c_begin = (ew >> 2) * COLS_PER_WARP, c_end = c_begin + COLS_PER_WARP;
         float* stg = reinterpret_cast<float*>(gen_base + TC_STAGES * S::STAGE_BYTES) + ew * 32 * S::EPI_PITCH;
@@ -638,6 +752,7 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
             ++lt;
         }
         TR_END();
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -868,6 +983,10 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
         for (int64_t w = pair; w < p.work_items && ok; w += n_pairs) {
             const TileCoord tc = pair_tile_coord(p, w);
             if (tc.skip) continue;
+            // bias-gradient by-product: the B-splitter thread of column n sees every element of op(B)[:, n] of this tile's K range;
+            // the tiles of the first row panel cover every column exactly once per K slice
+            float colsum_acc = 0.0f;
+            const bool want_colsum = A_TM && B_MN && p.colsum != nullptr && tc.m0 == 0 && warp >= 6;
             for (int i = 0; i < tc.nkb; ++i, ++it) {
                 const int s = it % NST;
                 const uint32_t ph = (it / NST) & 1u;
@@ -885,10 +1004,16 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                     uint8_t* st = gen_base + s * S::STAGE_BYTES;
                     if (warp < 6) {  // A rows of this warp's TMEM lane quarter
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#ifdef GCB_TC_TRACE
+                        if (!(p.dbg & 2))
+#endif
                         split_a_to_tmem<A_MN>(st, tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + S::A_TMEM_COL0 + s * 32, 32 * (warp & 3) + lane);
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     } else {
-                        split_hybrid<B_MN, BN / 2>(st + S::B_OFF, st + S::B_OFF + S::B_BYTES, t);
+#ifdef GCB_TC_TRACE
+                        if (!(p.dbg & 1))
+#endif
+                        split_hybrid<B_MN, BN / 2>(st + S::B_OFF, st + S::B_OFF + S::B_BYTES, t, want_colsum ? &colsum_acc : nullptr);
                     }
                 } else if (p.split_mode == 2) {
                     uint8_t* st = gen_base + s * S::STAGE_BYTES;
@@ -901,6 +1026,13 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive_on_cta(conv_bar(s), 0);  // the leader's barrier counts both CTAs' splitter warps
+            }
+            if (want_colsum && ok) {
+                const int64_t n = (int64_t)tc.n0 + 128 * (int)rank + t;
+                if (n < p.N) {
+                    if (p.splits > 1) p.colsum_partial[(int64_t)tc.split * p.N + n] = colsum_acc;  // summed over the K slices, in slice order, by the reduce kernel
+                    else p.colsum[n] = p.colsum_accumulate ? p.colsum[n] + colsum_acc : colsum_acc;
+                }
             }
         }
         TR_END();
@@ -945,6 +1077,9 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
             for (int c = c_begin; c < c_end; ++c) {
                 const int64_t nb = (int64_t)tc.n0 + 32 * c;
                 if (nb >= p.N) break;
+#ifdef GCB_TC_TRACE
+                if (p.dbg & 4) break;
+#endif
                 const bool blk_fast = vec_ok && mrow0 + 32 <= p.M && nb + 32 <= p.N;  // whole 32 x 32 block in bounds
                 float4 gp[8];  // GELU-backward epilogue: the block's pre-activations are requested before the accumulator is read
                 if (gelu_pre && blk_fast) {
@@ -1012,8 +1147,15 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
 
 // C = alpha * sum_s partial[s] + beta * C + bias, slices added in ascending order
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(float* __restrict__ C, const float* __restrict__ partial, const float* __restrict__ bias, int64_t M, int64_t N, int64_t ldc, int splits,
-                                                            float alpha, float beta) {
+                                                            float alpha, float beta, float* __restrict__ colsum, const float* __restrict__ colsum_partial, int colsum_accumulate) {
     const int64_t total = M * N;
+    if (colsum != nullptr) {  // the column sums of op(B), one partial per K slice
+        for (int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; n < N; n += (int64_t)gridDim.x * blockDim.x) {
+            float s = 0.0f;
+            for (int k = 0; k < splits; ++k) s += colsum_partial[(int64_t)k * N + n];
+            colsum[n] = colsum_accumulate ? colsum[n] + s : s;
+        }
+    }
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t m = i / N, n = i - m * N;
         float s = 0.0f;
@@ -1072,6 +1214,16 @@ static bool encode_operand(EncodeTiledFn enc, CUtensorMap* map, const float* ptr
     return r == CUDA_SUCCESS;
 }
 
+// Tensor map over the output (or an array laid out like it) in 32 x 32 blocks with the 128-byte swizzle: (column, row, batch inner, batch outer).
+static bool encode_output(EncodeTiledFn enc, CUtensorMap* map, const float* ptr, int64_t M, int64_t N, int64_t ld, int64_t s_in, int64_t s_out, int64_t n_in, int64_t n_out) {
+    const cuuint64_t row_bytes = (cuuint64_t)ld * 4;
+    cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)n_in, (cuuint64_t)n_out};
+    cuuint64_t strides[3] = {row_bytes, n_in > 1 ? (cuuint64_t)s_in * 4 : row_bytes * (cuuint64_t)M, n_out > 1 ? (cuuint64_t)s_out * 4 : row_bytes * (cuuint64_t)M};
+    cuuint32_t box[4] = {32u, 32u, 1u, 1u}, estr[4] = {1, 1, 1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool gemm_tc_eligible(bool ta, bool tb, const GemmArgs& g) {
     auto ok4 = [](int64_t v) { return v % 4 == 0; };
     if (g.K < 1 || g.M < 1 || g.N < 1) return false;
@@ -1088,14 +1240,14 @@ bool gemm_tc_eligible(bool ta, bool tb, const GemmArgs& g) {
 }
 
 template <int BN, bool A_TM>
-static int launch_bn(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid) {
+static int launch_bn(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& mp, const TcParams& p, dim3 grid) {
     const size_t smem = TcSmem<BN, A_TM>::TOTAL;
 #define GCB_TC(AM, BMN)                                                                                                   \
     do {                                                                                                                  \
         auto kfn = gemm_tc_kernel<BN, AM, BMN, A_TM>;                                                                     \
         static bool attr_done[kMaxDevices] = {}; /* function attributes belong to a device, not to the process */       \
         if (!attr_done[ctx->device]) { GCB_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_done[ctx->device] = true; } \
-        kfn<<<grid, TcSmem<BN, A_TM>::THREADS, smem, ctx->stream>>>(ma, mb, p);                                                          \
+        kfn<<<grid, TcSmem<BN, A_TM>::THREADS, smem, ctx->stream>>>(ma, mb, mc, mp, p);                                                  \
     } while (0)
     // A "transposed" (stored K x M) is MN-major; B "normal" (stored K x N) is MN-major
     if (ta && !tb) GCB_TC(true, true);
@@ -1165,9 +1317,17 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     p.tiles_m = use_pair ? (int)((g.M + 255) / 256) : (int)((g.M + TC_BM - 1) / TC_BM);
     p.k_blocks_total = (int)((g.K + TC_BK - 1) / TC_BK);
     p.status = ctx->d_status;
+#ifdef GCB_TC_TRACE
+    p.dbg = getenv("GRADC_TC_DBG") ? atoi(getenv("GRADC_TC_DBG")) : 0;
+#endif
     p.sm_probs = g.sm_probs; p.sm_rowdot = g.sm_rowdot; p.sm_scale = g.sm_scale;
     p.gelu_pre = g.gelu_pre; p.gelu_act = g.gelu_act;
     if ((g.gelu_pre || g.gelu_act) && !use_pair) return GCB_UNSUPPORTED;  // only the pair kernel carries this epilogue; the caller applies it as a second pass instead
+    static const int pair_tmem_env = [] { const char* e = getenv("GRADC_TC_PAIR_ATMEM"); return e ? atoi(e) : 1; }();
+    const bool pair_a_tmem = pair_tmem_env != 0 && ctx->gemm_split_mode == 2;
+    // column sums of op(B): gathered by the B-splitter warps of the pair kernel (A through tensor memory) from B stored K x N
+    if (g.colsum && !(use_pair && pair_a_tmem && !tb && batches == 1)) return GCB_UNSUPPORTED;
+    p.colsum = g.colsum; p.colsum_accumulate = g.colsum_accumulate; p.colsum_partial = nullptr;
     const int64_t tiles = (int64_t)p.tiles_n * p.tiles_m * batches;
     if (tiles > 2147483647LL / 2) return GCB_UNSUPPORTED;
     // split-K when the tiles alone would leave SMs idle: pick the slice count with the lowest modelled time
@@ -1189,9 +1349,10 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     Scratch sc(ctx);
     p.partial = nullptr;
     if (splits > 1) {
-        int rc = sc.get(sizeof(float) * (size_t)splits * g.M * g.N);
+        int rc = sc.get(sizeof(float) * ((size_t)splits * g.M * g.N + (g.colsum ? (size_t)splits * g.N : 0)));
         if (rc) return rc;
         p.partial = sc.as<float>();
+        if (g.colsum) p.colsum_partial = p.partial + (size_t)splits * g.M * g.N;
     }
     p.batches = (int)batches;
     p.causal = g.causal;
@@ -1204,17 +1365,26 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     p.split_mode = ctx->gemm_split_mode;
     static const int a_tmem_env = [] { const char* e = getenv("GRADC_TC_ATMEM"); return e ? atoi(e) : 1; }();
     const bool a_tmem = a_tmem_env != 0 && p.split_mode == 2 && BN <= 128;  // narrow tiles: A through tensor memory
-    static const int pair_tmem_env = [] { const char* e = getenv("GRADC_TC_PAIR_ATMEM"); return e ? atoi(e) : 1; }();
     dim3 grid((unsigned)std::min<int64_t>(p.work_items, (int64_t)kSMs * (BN == 64 ? 2 : 1)), 1, 1);
     p.loop_end = g.causal >= 2 ? (p.work_items + grid.x - 1) / grid.x * grid.x : p.work_items;  // snake order: whole rounds
     // one group = about one round of the grid: with the snake order a CTA then alternates between a heavy and the matching
     // light row tile, and a group's B operands (a few MB) are reused while they are still in L2
     p.group_batches = (int)std::max<int64_t>(1, std::min<int64_t>(batches, (int64_t)grid.x / std::max(1, p.tiles_m * p.tiles_n)));
+    // the 256-wide single-CTA kernel writes C (and reads the probabilities of the dS epilogue) through TMA when their layout allows it
+    CUtensorMap mc = ma, mp = ma;  // placeholders where unused
+    p.c_tma = 0;
+    static const int c_tma_env = [] { const char* e = getenv("GRADC_TC_EPI_TMA"); return e ? atoi(e) : 1; }();
+    if (c_tma_env != 0 && !use_pair && BN == 256 && splits == 1 && g.beta == 0.0f && aligned16(g.C) && g.ldc % 4 == 0 && (g.batch_inner == 1 || (g.c_si % 4 == 0 && g.c_si > 0)) &&
+        (g.batch_outer == 1 || (g.c_so % 4 == 0 && g.c_so > 0)) && (g.sm_probs == nullptr || aligned16(g.sm_probs))) {
+        bool ok = encode_output(enc, &mc, g.C, g.M, g.N, g.ldc, g.c_si, g.c_so, g.batch_inner, g.batch_outer);
+        if (ok && g.sm_probs) ok = encode_output(enc, &mp, g.sm_probs, g.M, g.N, g.ldc, g.c_si, g.c_so, g.batch_inner, g.batch_outer);
+        p.c_tma = ok ? 1 : 0;
+    }
     int rc;
-    if (use_pair) rc = (pair_tmem_env != 0 && p.split_mode == 2) ? launch_pair<true>(ctx, ta, tb, ma, mb, p) : launch_pair<false>(ctx, ta, tb, ma, mb, p);
-    else if (BN == 256) rc = launch_bn<256, false>(ctx, ta, tb, ma, mb, p, grid);
-    else if (BN == 128) rc = a_tmem ? launch_bn<128, true>(ctx, ta, tb, ma, mb, p, grid) : launch_bn<128, false>(ctx, ta, tb, ma, mb, p, grid);
-    else rc = a_tmem ? launch_bn<64, true>(ctx, ta, tb, ma, mb, p, grid) : launch_bn<64, false>(ctx, ta, tb, ma, mb, p, grid);
+    if (use_pair) rc = pair_a_tmem ? launch_pair<true>(ctx, ta, tb, ma, mb, p) : launch_pair<false>(ctx, ta, tb, ma, mb, p);
+    else if (BN == 256) rc = launch_bn<256, false>(ctx, ta, tb, ma, mb, mc, mp, p, grid);
+    else if (BN == 128) rc = a_tmem ? launch_bn<128, true>(ctx, ta, tb, ma, mb, mc, mp, p, grid) : launch_bn<128, false>(ctx, ta, tb, ma, mb, mc, mp, p, grid);
+    else rc = a_tmem ? launch_bn<64, true>(ctx, ta, tb, ma, mb, mc, mp, p, grid) : launch_bn<64, false>(ctx, ta, tb, ma, mb, mc, mp, p, grid);
     if (rc) return rc;
     const char* family = use_pair ? (g.gelu_act ? "gemm_tc_pair_gelu_fwd" : g.gelu_pre ? "gemm_tc_pair_gelu_bwd" : "gemm_tc_pair")
                          : BN == 256 ? (g.sm_probs ? "gemm_tc_256_softmax_bwd" : "gemm_tc_256") : BN == 128 ? "gemm_tc_128" : "gemm_tc_64";
@@ -1222,7 +1392,8 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     if (rc) return rc;
     if (splits > 1) {
         const int64_t total = g.M * g.N;
-        splitk_reduce_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)kSMs * 8), 256, 0, ctx->stream>>>(g.C, p.partial, g.bias, g.M, g.N, g.ldc, splits, g.alpha, g.beta);
+        splitk_reduce_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)kSMs * 8), 256, 0, ctx->stream>>>(g.C, p.partial, g.bias, g.M, g.N, g.ldc, splits, g.alpha, g.beta, g.colsum,
+                                                                                                                              p.colsum_partial, g.colsum_accumulate);
         rc = after_launch(ctx, "splitk_reduce");
         if (rc) return rc;
     }

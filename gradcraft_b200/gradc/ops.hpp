@@ -553,6 +553,7 @@ public:
         gcb_ctx* c = ctx_of(gc);
         MatView w;
         as_matview(m_w, w);
+        bool bias_done = false;
         if (m_x.requires_grad()) {  // dX[M,K] = dY[M,N] . W^T
             // x = gelu(pre): the GEMM applies gelu'(pre) in its epilogue and hands the result to pre directly; x itself then
             // receives no gradient here, so the sweep skips the GELU node (any other consumer of x still goes through it)
@@ -580,14 +581,20 @@ public:
                 gcb_check(gcb_gemm_f32(c, GCB_OP_T, GCB_OP_N, m_N, m_K, m_M, 1.0f, gc.data_ptr(), m_N, m_x.data_ptr(), m_K, acc ? 1.0f : 0.0f, dE.data_ptr(), m_K, nullptr), "matmul dW (tied)");
             } else if (!w.transposed) {  // dW[K,N] = X^T . dY
                 auto [dw, acc] = m_w.grad_target();
-                gcb_check(gcb_gemm_f32(c, GCB_OP_T, GCB_OP_N, m_K, m_N, m_M, 1.0f, m_x.data_ptr(), m_K, gc.data_ptr(), m_N, acc ? 1.0f : 0.0f, dw.data_ptr(), m_N, nullptr), "matmul dW");
+                if (m_b._get_state() != nullptr && m_b.requires_grad()) {  // the bias gradient is the column sum of the same dY: one pass over it serves both
+                    auto [db, acc_b] = m_b.grad_target();
+                    gcb_check(gcb_gemm_colsum_f32(c, GCB_OP_T, m_K, m_N, m_M, 1.0f, m_x.data_ptr(), m_K, gc.data_ptr(), acc ? 1.0f : 0.0f, dw.data_ptr(), m_N, db.data_ptr(), acc_b ? 1 : 0), "matmul dW + bias gradient");
+                    bias_done = true;
+                } else {
+                    gcb_check(gcb_gemm_f32(c, GCB_OP_T, GCB_OP_N, m_K, m_N, m_M, 1.0f, m_x.data_ptr(), m_K, gc.data_ptr(), m_N, acc ? 1.0f : 0.0f, dw.data_ptr(), m_N, nullptr), "matmul dW");
+                }
             } else {  // generic transposed view: produce the view's own gradient (K x N, dense) and let the view node route it
                 Tensor<float> dw({m_K, m_N}, gc.device(), uninitialized);
                 gcb_check(gcb_gemm_f32(c, GCB_OP_T, GCB_OP_N, m_K, m_N, m_M, 1.0f, m_x.data_ptr(), m_K, gc.data_ptr(), m_N, 0.0f, dw.data_ptr(), m_N, nullptr), "matmul dW");
                 push_grad(m_w, dw);
             }
         }
-        if (m_b._get_state() != nullptr && m_b.requires_grad()) {
+        if (!bias_done && m_b._get_state() != nullptr && m_b.requires_grad()) {
             auto [db, acc] = m_b.grad_target();
             gcb_check(gcb_reduce_rows_f32(c, db.data_ptr(), gc.data_ptr(), m_M, m_N, acc ? 1 : 0), "bias gradient");
         }

@@ -145,6 +145,13 @@ GCB_API int gcb_sum_squares_f32(gcb_ctx* ctx, float* out_scalar, const float* in
  * for shapes TMA cannot address. */
 GCB_API int gcb_gemm_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda,
                  const float* B, int64_t ldb, float beta, float* C, int64_t ldc, const float* bias);
+/* C[M,N] = alpha * op(A)[M,K] * B[K,N] + beta * C together with the column sums of B: colsum[n] (+)= sum_k B[k, n], B dense
+ * (ldb = N).  With A = x (stored tokens x in, op T) and B = dy this is a linear layer's weight gradient dW = x^T dy and its
+ * bias gradient db = sum over tokens of dy from one pass over dy: NormalMatMulNode::backward (math_nodes.hpp:475-535)
+ * followed by AddNode::backward -> unbroadcast_grad (core/detail/tensor_detail.hpp:15-33).  Deterministic (fixed summation
+ * order).  Shapes the tcgen05 CTA-pair kernel does not take run the product and gcb_reduce_rows_f32 one after the other. */
+GCB_API int gcb_gemm_colsum_f32(gcb_ctx* ctx, int op_a, int64_t M, int64_t N, int64_t K, float alpha, const float* A, int64_t lda, const float* B, float beta, float* C, int64_t ldc,
+                        float* colsum, int colsum_accumulate);
 /* Batched with two-level batch strides (batch index = outer * batch_inner + inner) so that head-sliced
  * (B, T, H, D) views are consumed in place instead of through contiguous() copies. */
 GCB_API int gcb_gemm_batched_f32(gcb_ctx* ctx, int op_a, int op_b, int64_t M, int64_t N, int64_t K, float alpha,

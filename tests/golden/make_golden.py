@@ -74,10 +74,11 @@ DIGEST_CASES = {"mid_lngelu"}
 # noise by the third step: the numpy restatement, which reduces in float64, reproduces the reference's weights after three
 # steps to 1.2e-7 and its first-step gradients to 2e-5, but differs from its third-step gradients by up to 1.07e-4.
 LAST_STEP_TOL = {"mid_lngelu": 3e-4}
-# Tolerance of the clipper's global gradient norm (default 1e-4).  The reference adds the 1.9 M squares of this case serially
-# in fp32: its recorded norm at step 1 (6.11739) is 2.4e-4 below the norm of its own recorded gradients summed in float64
-# (6.118873, which the digest's per-tensor sums of squares give and which the numpy restatement reproduces to 2e-8).
-NORM_TOL = {"mid_lngelu": 5e-4}
+# Tolerance of the clipper's global gradient norm against the norm the reference recorded (default 1e-4).  The reference adds
+# the 1.9 M squares of this case serially in fp32: its recorded norms (6.11739 at step 1, 3.23069 at step 3) are 2.4e-4 and
+# 7.1e-4 below the norms of its own recorded gradients summed in float64 (6.118873 and 3.232969, which the digest's per-tensor
+# sums of squares give).  Tests hold the computed norm to those float64 norms at 1e-4 and to the recorded ones at this bound.
+NORM_TOL = {"mid_lngelu": 1.5e-3}
 DIGEST_STRIDE = 29  # every 29th element of each flattened tensor is kept
 
 

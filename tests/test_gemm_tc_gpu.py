@@ -425,3 +425,50 @@ def test_fused_epilogues_take_the_scalar_path_for_side_arrays_off_a_16_byte_boun
     ctx.sync()
     assert ctx.ctx_launch_count_named(b"gemm_tc_pair_gelu_bwd") >= 2
     assert torch.equal(out_a, out_b)
+
+
+@pytest.mark.parametrize("Kin,Nout,Mtok,family", [(1024, 1024, 8192, "gemm_tc_pair"), (512, 768, 4096, "gemm_tc_pair"), (256, 1024, 300, "gemm_tc_pair"), (96, 80, 200, None), (1024, 100, 4096, None)])
+def test_weight_gradient_with_bias_gradient_from_one_pass(env, Kin, Nout, Mtok, family):
+    """dW = x^T dy and db = column sums of dy from one call, against float64: shapes that run the CTA-pair kernel with and
+    without K slices (the B-splitter warps gather the sums), and shapes that fall back to the product plus a row reduction.
+    Overwrite and accumulate forms; the result is run-to-run identical."""
+    ctx, torch, capi = env
+    x, dy = rnd(100, Mtok, Kin), rnd(101, Mtok, Nout) * 1e-2 + 3e-3
+    dW0, db0 = rnd(102, Kin, Nout) * 1e-2, rnd(103, Nout) * 1e-2
+    X, DY = torch.from_numpy(x).cuda(), torch.from_numpy(dy).cuda()
+    ref_w = x.astype(np.float64).T @ dy.astype(np.float64)
+    ref_b = dy.astype(np.float64).sum(0)
+    ctx.ctx_set_gemm_engine(0)
+    try:
+        before = ctx.ctx_launch_count_named(b"gemm_tc_pair")
+        dW, db = torch.full((Kin, Nout), float("nan"), device="cuda"), torch.full((Nout,), float("nan"), device="cuda")
+        ctx.gemm_colsum_f32(1, Kin, Nout, Mtok, 1.0, X, Kin, DY, 0.0, dW, Nout, db, 0)
+        ctx.sync()
+        if family:
+            assert ctx.ctx_launch_count_named(b"gemm_tc_pair") == before + 1
+        assert max_abs_rel(dW.cpu().numpy(), ref_w) < TOL and max_abs_rel(db.cpu().numpy(), ref_b) < 1e-5
+        first = (dW.clone(), db.clone())
+        dW2, db2 = torch.from_numpy(dW0).cuda(), torch.from_numpy(db0).cuda()
+        ctx.gemm_colsum_f32(1, Kin, Nout, Mtok, 1.0, X, Kin, DY, 1.0, dW2, Nout, db2, 1)
+        ctx.sync()
+        assert max_abs_rel(dW2.cpu().numpy(), ref_w + dW0) < TOL and max_abs_rel(db2.cpu().numpy(), ref_b + db0) < 1e-5
+        dW3, db3 = torch.empty_like(dW), torch.empty_like(db)
+        ctx.gemm_colsum_f32(1, Kin, Nout, Mtok, 1.0, X, Kin, DY, 0.0, dW3, Nout, db3, 0)
+        ctx.sync()
+        assert torch.equal(dW3, first[0]) and torch.equal(db3, first[1])
+    finally:
+        ctx.ctx_set_gemm_engine(2)
+
+
+def test_bias_gradient_rides_on_the_pair_kernel_for_the_step_shapes(env):
+    """At a linear layer's backward shape the fused call launches the pair GEMM (+ its K-slice reduction) and no row-reduction kernel."""
+    ctx, torch, capi = env
+    Kin, Nout, Mtok = 1024, 1024, 8192
+    X, DY = torch.from_numpy(rnd(110, Mtok, Kin)).cuda(), torch.from_numpy(rnd(111, Mtok, Nout)).cuda()
+    dW, db = torch.empty(Kin, Nout, device="cuda"), torch.empty(Nout, device="cuda")
+    pair0, red0 = ctx.ctx_launch_count_named(b"gemm_tc_pair"), ctx.ctx_launch_count_named(b"reduce_rows")
+    ctx.gemm_colsum_f32(1, Kin, Nout, Mtok, 1.0, X, Kin, DY, 0.0, dW, Nout, db, 0)
+    ctx.sync()
+    assert ctx.ctx_launch_count_named(b"gemm_tc_pair") == pair0 + 1
+    assert ctx.ctx_launch_count_named(b"reduce_rows") == red0
+    assert max_abs_rel(db.cpu().numpy(), DY.double().sum(0).cpu().numpy()) < 1e-5

@@ -45,8 +45,8 @@ def run_case(name, engine=None, split_mode=None, families=()):
             norm = tr.optimizer_step(want_norm=True)
             if clip > 0:
                 assert abs(norm - float(gold["norm"][step - 1])) / float(gold["norm"][step - 1]) < NORM_TOL.get(name, 1e-4)
-                if is_digest and step == 1:  # the norm of the reference's own gradients, summed in float64
-                    exact = float(np.sqrt(sum(v[1] for v in split_prefix(gold, "stat/grads1/").values())))
+                if is_digest and step in (1, steps):  # the norm of the reference's own gradients, summed in float64
+                    exact = float(np.sqrt(sum(v[1] for v in split_prefix(gold, "stat/grads%d/" % step).values())))
                     assert abs(norm - exact) / exact < 1e-4, (norm, exact)
         rel = np.abs(np.array(losses) - gold["loss"]) / np.abs(gold["loss"])
         assert rel.max() < 1e-5, (rel, losses, gold["loss"])
