@@ -10,6 +10,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/gradc_b200.h"
@@ -55,6 +56,13 @@ struct Arena {
     void destroy();
 };
 
+// A weight matrix whose BF16 companions for the split-fp32 GEMM are kept in global memory (twins.cu).
+struct WeightTwin {
+    const float* base = nullptr;
+    int64_t rows = 0, cols = 0;      // as stored (dense, row-major)
+    void *kn = nullptr, *nk = nullptr;  // companions for the roles "B stored K x N" and "B stored N x K"
+};
+
 }  // namespace gcb
 
 struct gcb_ctx {
@@ -83,6 +91,11 @@ struct gcb_ctx {
     std::vector<cudaEvent_t> prof_events;
     size_t prof_used = 0;
     double prof_flops = 0.0;
+    // pre-split weights (twins.cu)
+    std::vector<gcb::WeightTwin> twins;
+    std::unordered_map<const float*, int> twin_index;
+    const char *twins_lo = nullptr, *twins_hi = nullptr;  // address range covering every registered weight
+    bool twins_dirty = false;
     std::mutex mu;
 };
 
@@ -113,6 +126,16 @@ inline int after_launch(gcb_ctx* ctx, const char* what, int n = 1) {
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Every entry point that writes device memory a caller could also use as a registered weight reports the range here: an
+// overlap marks the pre-split companions stale (they are recomputed before the next GEMM that needs one).
+inline void note_write(gcb_ctx* ctx, const void* p, size_t bytes) {
+    if (ctx->twins_lo == nullptr || ctx->twins_dirty) return;
+    const char* b = static_cast<const char*>(p);
+    if (b < ctx->twins_hi && b + bytes > ctx->twins_lo) ctx->twins_dirty = true;
+}
+int twins_lookup(gcb_ctx* ctx, const float* base, bool stored_n_by_k, int64_t N, int64_t K, int64_t ldb, const void** out);
+size_t twin_bytes(int64_t N, int64_t K);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }

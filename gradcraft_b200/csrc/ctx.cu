@@ -307,6 +307,7 @@ int gcb_arena_set_limit(gcb_ctx* ctx, size_t bytes) {
 
 int gcb_copy_h2d(gcb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     GCB_REQUIRE(ctx && (bytes == 0 || (dst && src)), "gcb_copy_h2d: NULL argument");
+    note_write(ctx, dst, bytes);
     GCB_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
     GCB_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
     return GCB_OK;
@@ -321,6 +322,7 @@ int gcb_copy_d2h(gcb_ctx* ctx, void* dst, const void* src, size_t bytes) {
 }
 int gcb_copy_h2d_async(gcb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     GCB_REQUIRE(ctx && (bytes == 0 || (dst && src)), "gcb_copy_h2d_async: NULL argument");
+    note_write(ctx, dst, bytes);
     GCB_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
     return GCB_OK;
 }
@@ -331,6 +333,7 @@ int gcb_copy_d2h_async(gcb_ctx* ctx, void* dst, const void* src, size_t bytes) {
 }
 int gcb_copy_d2d(gcb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     GCB_REQUIRE(ctx && (bytes == 0 || (dst && src)), "gcb_copy_d2d: NULL argument");
+    note_write(ctx, dst, bytes);
     GCB_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return GCB_OK;
 }
@@ -347,6 +350,7 @@ int gcb_host_free_pinned(void* p) {
 int gcb_fill_f32(gcb_ctx* ctx, float* p, float v, int64_t n) {
     GCB_REQUIRE(ctx && n >= 0 && (n == 0 || p), "gcb_fill_f32: bad arguments");
     if (n == 0) return GCB_OK;
+    note_write(ctx, p, sizeof(float) * (size_t)n);
     if (v == 0.0f) { GCB_CHECK_CUDA(cudaMemsetAsync(p, 0, n * sizeof(float), ctx->stream)); return GCB_OK; }
     const int64_t n4 = aligned16(p) ? (n >> 2) : 0;
     int64_t blocks = ((n4 ? n4 : n) + 255) / 256;
@@ -365,6 +369,7 @@ int gcb_fill_arange_i64(gcb_ctx* ctx, int64_t* p, int64_t start, int64_t step, i
 }
 int gcb_set_scalar_f32(gcb_ctx* ctx, float* p, float v) {
     GCB_REQUIRE(ctx && p, "gcb_set_scalar_f32: NULL argument");
+    note_write(ctx, p, sizeof(float));
     // the value travels by value inside the memset node: no pageable host buffer to outlive
     uint32_t bits;
     memcpy(&bits, &v, 4);

@@ -317,24 +317,28 @@ int gcb_unary_f32(gcb_ctx* ctx, int op, float* out, const float* in, int64_t n) 
     GCB_REQUIRE(ctx && n >= 0 && (n == 0 || (out && in)), "gcb_unary_f32: bad arguments");
     GCB_REQUIRE(op >= GCB_U_IDENTITY && op <= GCB_U_TANH, "gcb_unary_f32: unknown op %d", op);
     EwPtrs<1, 1> p{{in}, {out}};
+    note_write(ctx, out, sizeof(float) * (size_t)n);
     return ew_launch(ctx, "unary_f32", p, n, UnaryOp{op});
 }
 int gcb_binary_f32(gcb_ctx* ctx, int op, float* out, const float* a, const float* b, int64_t n) {
     GCB_REQUIRE(ctx && n >= 0 && (n == 0 || (out && a && b)), "gcb_binary_f32: bad arguments");
     GCB_REQUIRE(op >= GCB_B_ADD && op <= GCB_B_IDIV, "gcb_binary_f32: unknown op %d", op);
     EwPtrs<2, 1> p{{a, b}, {out}};
+    note_write(ctx, out, sizeof(float) * (size_t)n);
     return ew_launch(ctx, "binary_f32", p, n, BinaryOp{op});
 }
 int gcb_binary_scalar_f32(gcb_ctx* ctx, int op, float* out, const float* a, float b, int64_t n) {
     GCB_REQUIRE(ctx && n >= 0 && (n == 0 || (out && a)), "gcb_binary_scalar_f32: bad arguments");
     GCB_REQUIRE(op >= GCB_B_ADD && op <= GCB_B_IDIV, "gcb_binary_scalar_f32: unknown op %d", op);
     EwPtrs<1, 1> p{{a}, {out}};
+    note_write(ctx, out, sizeof(float) * (size_t)n);
     return ew_launch(ctx, "binary_scalar_f32", p, n, BinaryScalarOp{op, b});
 }
 int gcb_binary_rowvec_f32(gcb_ctx* ctx, int op, float* out, const float* a, const float* vec, int64_t rows, int64_t cols) {
     GCB_REQUIRE(ctx && rows >= 0 && cols >= 0, "gcb_binary_rowvec_f32: bad arguments");
     if (rows * cols == 0) return GCB_OK;
     GCB_REQUIRE(out && a && vec, "gcb_binary_rowvec_f32: NULL pointer");
+    note_write(ctx, out, sizeof(float) * (size_t)(rows * cols));
     const bool v4 = (cols % 4 == 0) && aligned16(out) && aligned16(a) && aligned16(vec);
     int64_t work = v4 ? rows * cols / 4 : rows * cols;
     int64_t blocks = std::min<int64_t>((work + 255) / 256, kSMs * 8);
@@ -362,6 +366,7 @@ int gcb_binary_strided_f32(gcb_ctx* ctx, int op, int ndim, const int64_t* shape,
     if (total == 0) return GCB_OK;
     int64_t blocks = std::min<int64_t>((total + 255) / 256, kSMs * 8);
     cudaSetDevice(ctx->device);
+    if (ctx->twins_lo != nullptr) ctx->twins_dirty = true;  // a strided destination has no simple range: any registered weight may be hit
     strided_kernel<true, false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(out, a, b, m, total, op);
     return after_launch(ctx, "binary_strided_f32");
 }
@@ -372,6 +377,7 @@ int gcb_copy_strided_f32(gcb_ctx* ctx, int ndim, const int64_t* shape, float* ou
     if (rc) return rc;
     if (total == 0) return GCB_OK;
     int64_t blocks = std::min<int64_t>((total + 255) / 256, kSMs * 8);
+    if (ctx->twins_lo != nullptr) ctx->twins_dirty = true;  // strided destination: see gcb_binary_strided_f32
     cudaSetDevice(ctx->device);
     if (accumulate) strided_kernel<false, true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(out, in, nullptr, m, total, 0);
     else strided_kernel<false, false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(out, in, nullptr, m, total, 0);
@@ -463,6 +469,7 @@ int gcb_adamw_step_f32(gcb_ctx* ctx, float* w, float* m, float* v, const float* 
     GCB_REQUIRE(ctx && n >= 0 && (n == 0 || (w && m && v && g)), "gcb_adamw_step_f32: bad arguments");
     GCB_REQUIRE(b1p < 1.0f && b2p < 1.0f, "gcb_adamw_step_f32: beta powers must already be advanced (< 1)");
     EwPtrs<4, 3> p{{w, m, v, g}, {w, m, v}};
+    note_write(ctx, w, sizeof(float) * (size_t)n);
     return ew_launch(ctx, "adamw_step", p, n, AdamWTensorOp{make_adamw(lr, b1, b2, b1p, b2p, wd, eps, gscale), !no_decay});
 }
 int gcb_adamw_arena_f32(gcb_ctx* ctx, float* w, float* m, float* v, const float* g, const uint8_t* mask, int64_t n, float lr, float b1, float b2, float b1p, float b2p, float wd, float eps, float gscale) {
@@ -473,6 +480,7 @@ int gcb_adamw_arena_f32(gcb_ctx* ctx, float* w, float* m, float* v, const float*
     const int64_t chunks = (n + GCB_ADAMW_CHUNK - 1) / GCB_ADAMW_CHUNK;
     int64_t blocks = std::min<int64_t>(chunks, kSMs * 8);
     cudaSetDevice(ctx->device);
+    note_write(ctx, w, sizeof(float) * (size_t)n);
     adamw_arena_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(w, m, v, g, mask, n, chunks, make_adamw(lr, b1, b2, b1p, b2p, wd, eps, gscale));
     return after_launch(ctx, "adamw_arena");
 }

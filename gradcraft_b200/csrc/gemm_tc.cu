@@ -53,6 +53,7 @@ struct TcParams {
                          // 1: three TF32 products; big stays as loaded — the tensor core ignores the 13 low mantissa bits — and small = rna_tf32(x - trunc(x));
                          // 0: as 1 with big = rna_tf32(x) written back, small = x - big (does not rely on the hardware's truncation)
     float* partial;      // [splits][M][N] when splits > 1
+    int b_twin;              // pair kernel: the BF16 companions of B come pre-split from global memory (map_t), the B-splitter warps idle
     int c_tma;               // 256-wide single-CTA kernel: C leaves (and the probabilities arrive) through TMA on swizzled 32 x 32 blocks in shared memory
     float* colsum;           // column sums of op(B) (see GemmArgs), or NULL: pair kernel with B stored K x N only
     float* colsum_partial;   // [splits][N] when splits > 1
@@ -64,7 +65,7 @@ struct TcParams {
     float sm_scale;
     int* status;
 #ifdef GCB_TC_TRACE
-    int dbg;  // timing experiments (results are wrong): 1 B is not split, 2 A is not moved to tensor memory, 4 the epilogue stores nothing
+    int dbg;  // timing experiments (results are wrong): 1 B is not split, 2 A is not split / moved to tensor memory, 4 the epilogue does nothing, 8 it does everything but the store
 #endif
 };
 
@@ -91,6 +92,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
     asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
@@ -530,6 +534,10 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
                         }
                     }
                 };
+#ifdef GCB_TC_TRACE
+                if (p.dbg & 3) {
+                } else
+#endif
                 if constexpr (A_TM) {
                     uint8_t* st = gen_base + s * S::STAGE_BYTES;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");  // the MMAs that read this TMEM stage last round have completed (empty -> TMA -> full)
@@ -590,6 +598,9 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
                 for (int j = 0; j < nchunks; ++j, ++nblk) {
+#ifdef GCB_TC_TRACE
+                    if (p.dbg & 4) break;
+#endif
                     const int c = c_begin + j;
                     const int64_t nb = (int64_t)tc.n0 + 32 * c;
                     const uint32_t b = nblk & 1u;
@@ -633,6 +644,9 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the block as written by these threads -> visible to the TMA unit
                     __syncwarp();
+#ifdef GCB_TC_TRACE
+                    if (!(p.dbg & 8))
+#endif
                     if (lane == 0) {
                         tma_store_4d(&map_c, blk_sh + b * 4096, (int)nb, m_blk, tc.b_in, tc.b_out);  // rows / columns beyond M / N are clipped by the unit
                         tma_store_commit();
@@ -841,7 +855,8 @@ __device__ __forceinline__ TileCoord pair_tile_coord(const TcParams& p, int64_t 
 }
 
 template <bool A_MN, bool B_MN, bool A_TM>
-__global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+__global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                                                    const __grid_constant__ CUtensorMap map_t, TcParams p) {
     using S = PairSmemT<A_TM>;
     constexpr int BN = S::BN, NST = S::STAGES, NACC = S::NACC;
     extern __shared__ uint8_t smem_raw[];
@@ -891,8 +906,11 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                     ok = TR_WAIT(mbar_wait(empty_bar(s), ph ^ 1u, p.status, 11));
                     if (!ok) break;
                     const uint32_t sa = base + s * S::STAGE_BYTES, sb = sa + S::B_OFF;
-                    mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES);
+                    const bool twin = A_TM && p.b_twin != 0;
+                    mbar_expect_tx(full_bar(s), S::A_BYTES + S::B_BYTES + (twin ? S::B_BYTES : 0));
                     const int k0 = (tc.kb0 + i) * TC_BK;
+                    // this CTA's 128 columns of the pre-split companions: 16 groups of 8 columns x 2 chunks of 8 k, big then small
+                    if (twin) tma_load_3d(sb + S::B_BYTES, &map_t, full_bar(s), (k0 >> 3) * 64, n0 >> 3, 0);
                     if (A_MN) {
                         if (p.a_chunked) tma_load_5d(sa, &map_a, full_bar(s), 0, k0, m0 / 32, tc.b_in, tc.b_out);
                         else
@@ -1013,6 +1031,7 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
 #ifdef GCB_TC_TRACE
                         if (!(p.dbg & 1))
 #endif
+                        if (!p.b_twin)  // otherwise the companions arrived with the tile
                         split_hybrid<B_MN, BN / 2>(st + S::B_OFF, st + S::B_OFF + S::B_BYTES, t, want_colsum ? &colsum_acc : nullptr);
                     }
                 } else if (p.split_mode == 2) {
@@ -1258,8 +1277,15 @@ static int launch_bn(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, cons
     return GCB_OK;
 }
 
+static int64_t pair_cap() {  // timing experiments (trace build): run fewer CTA pairs than fit
+#ifdef GCB_TC_TRACE
+    if (const char* e = getenv("GRADC_TC_MAX_PAIRS")) return atoi(e);
+#endif
+    return 1 << 30;
+}
+
 template <bool A_TM>
-static int launch_pair(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p) {
+static int launch_pair(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mt, const TcParams& p) {
     const size_t smem = PairSmemT<A_TM>::TOTAL;
     cudaLaunchConfig_t cfg = {};
     const int64_t pairs = std::min<int64_t>(p.work_items, kSMs / 2);
@@ -1286,8 +1312,8 @@ static int launch_pair(gcb_ctx* ctx, bool ta, bool tb, const CUtensorMap& ma, co
             if (mc < 1) { set_error("gemm (pair): no cluster of two CTAs fits on this device"); return GCB_UNSUPPORTED; }   \
             max_clusters[ctx->device] = mc;                                                                                 \
         }                                                                                                                   \
-        cfg.gridDim = dim3((unsigned)(2 * std::min<int64_t>(p.work_items, max_clusters[ctx->device])), 1, 1);               \
-        GCB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kfn, ma, mb, p));                                                           \
+        cfg.gridDim = dim3((unsigned)(2 * std::min<int64_t>(p.work_items, std::min<int64_t>(max_clusters[ctx->device], pair_cap()))), 1, 1); \
+        GCB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kfn, ma, mb, mt, p));                                                       \
     } while (0)
     if (ta && !tb) GCB_PAIR(true, true);
     else if (ta && tb) GCB_PAIR(true, false);
@@ -1370,6 +1396,24 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     // one group = about one round of the grid: with the snake order a CTA then alternates between a heavy and the matching
     // light row tile, and a group's B operands (a few MB) are reused while they are still in L2
     p.group_batches = (int)std::max<int64_t>(1, std::min<int64_t>(batches, (int64_t)grid.x / std::max(1, p.tiles_m * p.tiles_n)));
+    // B is a registered weight: its BF16 companions come pre-split from global memory (twins.cu)
+    CUtensorMap mt = ma;
+    p.b_twin = 0;
+    static const int twin_env = [] { const char* e = getenv("GRADC_TC_WEIGHT_TWINS"); return e ? atoi(e) : 1; }();
+    if (twin_env != 0 && use_pair && pair_a_tmem && batches == 1 && g.colsum == nullptr) {
+        const void* tw = nullptr;
+        int rc_t = twins_lookup(ctx, g.B, tb, g.N, g.K, g.ldb, &tw);
+        if (rc_t) return rc_t;
+        if (tw != nullptr) {
+            const cuuint64_t n_groups = (cuuint64_t)((g.N + 7) / 8), k_chunks = (cuuint64_t)(((g.K + 15) / 16) * 2);
+            cuuint64_t dims[3] = {k_chunks * 64, n_groups, 2};
+            cuuint64_t strides[2] = {k_chunks * 128, n_groups * k_chunks * 128};
+            cuuint32_t box[3] = {128u, 16u, 2u}, estr[3] = {1, 1, 1};
+            if (enc(&mt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(tw), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+                p.b_twin = 1;
+        }
+    }
     // the 256-wide single-CTA kernel writes C (and reads the probabilities of the dS epilogue) through TMA when their layout allows it
     CUtensorMap mc = ma, mp = ma;  // placeholders where unused
     p.c_tma = 0;
@@ -1381,7 +1425,7 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
         p.c_tma = ok ? 1 : 0;
     }
     int rc;
-    if (use_pair) rc = pair_a_tmem ? launch_pair<true>(ctx, ta, tb, ma, mb, p) : launch_pair<false>(ctx, ta, tb, ma, mb, p);
+    if (use_pair) rc = pair_a_tmem ? launch_pair<true>(ctx, ta, tb, ma, mb, mt, p) : launch_pair<false>(ctx, ta, tb, ma, mb, mt, p);
     else if (BN == 256) rc = launch_bn<256, false>(ctx, ta, tb, ma, mb, mc, mp, p, grid);
     else if (BN == 128) rc = a_tmem ? launch_bn<128, true>(ctx, ta, tb, ma, mb, mc, mp, p, grid) : launch_bn<128, false>(ctx, ta, tb, ma, mb, mc, mp, p, grid);
     else rc = a_tmem ? launch_bn<64, true>(ctx, ta, tb, ma, mb, mc, mp, p, grid) : launch_bn<64, false>(ctx, ta, tb, ma, mb, mc, mp, p, grid);

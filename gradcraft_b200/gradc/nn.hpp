@@ -260,6 +260,13 @@ public:
                 p->tensor() = std::move(leaf);
             }
             gcb_check(gcb_ctx_sync(c), "parameter upload");
+            // every weight matrix is a B operand of the forward GEMM (stored K x N) and of the dX GEMM (stored N x K): keep the BF16
+            // companions the split-fp32 engine needs pre-split in global memory instead of re-deriving them in every CTA
+            for (size_t i = 0; i < ordered.size(); ++i) {
+                const Tensor<T>& t = ordered[i].second->tensor();
+                if (t.shape().size() == 2 && t.shape()[0] >= 128 && t.shape()[1] >= 128 && t.shape()[1] % 4 == 0)
+                    gcb_check(gcb_weight_twins_register(c, t.data_ptr(), t.shape()[0], t.shape()[1]), "registering a weight's pre-split companions");
+            }
             if (const char* e = std::getenv("GRADC_ACCUM_STEPS")) arena->accum_expected = std::atoll(e);
         } else {
             throw std::runtime_error("Module::to(CUDA): float modules only");

@@ -134,6 +134,7 @@ struct ParamArena {
 
     ~ParamArena() {
         Backend& b = Backend::get();
+        if (w != nullptr && !device.is_cpu()) gcb_weight_twins_drop(b.ctx(device), w, sizeof(float) * (size_t)total);  // pre-split companions of the matrices in this arena
         b.release(w, device); b.release(g, device); b.release(m, device); b.release(v, device); b.release(decay_mask, device);
     }
     void begin_backward() {

@@ -203,6 +203,22 @@ GCB_API int gcb_rowdot_batched_f32(gcb_ctx* ctx, float* out, const float* a, int
                            const float* b, int64_t ldb, int64_t b_stride_outer, int64_t b_stride_inner,
                            int64_t rows, int64_t cols, int64_t batch_outer, int64_t batch_inner);
 
+/* Pre-split weights (no counterpart in the reference: cuBLAS in TF32 mode rounds operands on the fly, kernels_math.cu:27-36).
+ * The split-fp32 GEMM needs two BF16 companions of every operand tile; for the B operand they are normally derived inside the
+ * kernel, by every CTA that uses the tile.  A dense rows x cols matrix registered here keeps them in global memory in tile
+ * order, for both of its roles as op(B) (stored K x N: y = x W; stored N x K: dx = dy W^T), and the CTA-pair kernel fetches
+ * them by TMA instead — same values, so results are bit-identical with and without registration.
+ * The companions are recomputed lazily: gcb_copy_h2d / _async, gcb_copy_d2d, gcb_fill_f32, gcb_set_scalar_f32, the
+ * elementwise entry points and both AdamW entry points mark them stale when they write into a registered matrix, and the next
+ * GEMM that uses one recomputes all of them first (about 12 bytes of traffic per weight element).  A registered matrix that
+ * is modified in any other way (a kernel of the caller's own, a peer copy) must be followed by gcb_weight_twins_invalidate.
+ * gcb_weight_twins_drop forgets every registered matrix that starts inside [range_begin, range_begin + bytes) (all of
+ * them when range_begin is NULL) and must be called before that memory is freed or reused. */
+GCB_API int gcb_weight_twins_register(gcb_ctx* ctx, const float* W, int64_t rows, int64_t cols);
+GCB_API int gcb_weight_twins_drop(gcb_ctx* ctx, const void* range_begin, size_t bytes);
+GCB_API int gcb_weight_twins_invalidate(gcb_ctx* ctx);
+GCB_API int64_t gcb_weight_twins_count(gcb_ctx* ctx);
+
 /* Measurement aid (the reference times with std::chrono around whole loops, benchmarks/bench_kernels.cpp:10-27):
  * between begin and end every GEMM launch is bracketed by CUDA events on the compute stream; end synchronises and
  * returns the number of launches, their summed device time and their algorithmic FLOPs (2*M*N*K*batches). */

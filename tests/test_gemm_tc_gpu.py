@@ -472,3 +472,50 @@ def test_bias_gradient_rides_on_the_pair_kernel_for_the_step_shapes(env):
     assert ctx.ctx_launch_count_named(b"gemm_tc_pair") == pair0 + 1
     assert ctx.ctx_launch_count_named(b"reduce_rows") == red0
     assert max_abs_rel(db.cpu().numpy(), DY.double().sum(0).cpu().numpy()) < 1e-5
+
+
+@pytest.mark.parametrize("rows,cols,M", [(1024, 768, 4096), (1000, 520, 700), (256, 1024, 384)])
+def test_registered_weights_use_presplit_companions_with_identical_results(env, rows, cols, M):
+    """A weight registered with gcb_weight_twins_register keeps its BF16 companions pre-split in global memory; the CTA-pair
+    kernel then fetches them by TMA instead of deriving them in every CTA.  Same values, so the product is bit-identical with
+    and without registration, in both roles of the weight (y = x W and dx = dy W^T), with ragged edges; a write into the
+    weight through the library makes the next GEMM recompute the companions."""
+    ctx, torch, capi = env
+    w = rnd(120, rows, cols) * 0.05
+    x, dy = rnd(121, M, rows), rnd(122, M, cols) * 1e-2
+    W_plain, W_reg = torch.from_numpy(w).cuda(), torch.from_numpy(w).cuda()
+    X, DY = torch.from_numpy(x).cuda(), torch.from_numpy(dy).cuda()
+
+    def products(W):
+        y, dx = torch.full((M, cols), float("nan"), device="cuda"), torch.full((M, rows), float("nan"), device="cuda")
+        ctx.gemm_f32(0, 0, M, cols, rows, 1.0, X, rows, W, cols, 0.0, y, cols, None)
+        ctx.gemm_f32(0, 1, M, rows, cols, 1.0, DY, cols, W, cols, 0.0, dx, rows, None)
+        ctx.sync()
+        return y, dx
+
+    y0, dx0 = products(W_plain)
+    assert max_abs_rel(y0.cpu().numpy(), x.astype(np.float64) @ w.astype(np.float64)) < TOL
+    assert max_abs_rel(dx0.cpu().numpy(), dy.astype(np.float64) @ w.astype(np.float64).T) < TOL
+    n0 = ctx.weight_twins_count()
+    ctx.weight_twins_register(W_reg, rows, cols)
+    try:
+        assert ctx.weight_twins_count() == n0 + 1
+        pre0 = ctx.ctx_launch_count_named(b"presplit_weight")
+        y1, dx1 = products(W_reg)
+        assert ctx.ctx_launch_count_named(b"presplit_weight") == pre0 + 2 * (n0 + 1)  # both orientations, once
+        assert torch.equal(y1, y0) and torch.equal(dx1, dx0)
+        y2, dx2 = products(W_reg)
+        assert ctx.ctx_launch_count_named(b"presplit_weight") == pre0 + 2 * (n0 + 1)  # nothing was written: no recomputation
+        assert torch.equal(y2, y0)
+        # the weight changes through the library (as an optimizer step or a checkpoint load would change it)
+        w2 = (w * 1.5 + 0.01).astype(np.float32)
+        ctx.copy_h2d(W_reg, w2, w2.nbytes)
+        ctx.copy_h2d(W_plain, w2, w2.nbytes)
+        y3, dx3 = products(W_reg)
+        y4, dx4 = products(W_plain)
+        assert ctx.ctx_launch_count_named(b"presplit_weight") == pre0 + 4 * (n0 + 1)
+        assert torch.equal(y3, y4) and torch.equal(dx3, dx4)
+        assert max_abs_rel(y3.cpu().numpy(), x.astype(np.float64) @ w2.astype(np.float64)) < TOL
+    finally:
+        ctx.weight_twins_drop(W_reg, w.nbytes)
+    assert ctx.weight_twins_count() == n0
