@@ -403,7 +403,7 @@ def run_ours(args, rank, world, local_rank):
 
 
 # ---- fused backward kernels vs the HBM roofline -----------------------------------------------------------------------
-def kernel_suite(steps, warmup, device=0):
+def kernel_suite(steps, warmup, device=0, only="", small=False):
     """The bandwidth-bound kernels of the backward pass and the optimizer at the microbenchmark shapes, each timed alone with
     CUDA events (L2 flushed by a 256 MB write before every sample): {name: {ms, algorithmic_bytes, achieved_gbs,
     frac_of_hbm_peak}}.  Algorithmic bytes count every operand once."""
@@ -435,59 +435,72 @@ def kernel_suite(steps, warmup, device=0):
         return float(np.median(ts))
 
     out, notes = {}, {}
-    M, V = 16384, 32768
-    P = torch.rand(M, V, device="cuda")
-    P /= P.sum(-1, keepdim=True)
-    Tg = torch.randint(0, V, (M,), dtype=torch.int32, device="cuda")
-    out["softmax_ce_bwd [16384,32768]"] = (timeit(lambda i: ctx.softmax_ce_bwd_f32(P, P, Tg, capi.IDX_I32, 1.0, M, V, 0)), 2 * M * V * 4 + M * 4)
-    del P
+    want = lambda name: (not only) or only in name  # --only: run the kernels whose name contains the text (profiling runs)
+    M, V = (2048 if small else 16384), 32768  # --small: an eighth of the rows, for captures that must stay within a few GB
+    if want("softmax_ce"):
+        P = torch.rand(M, V, device="cuda")
+        P /= P.sum(-1, keepdim=True)
+        Tg = torch.randint(0, V, (M,), dtype=torch.int32, device="cuda")
+        out["softmax_ce_bwd [%d,32768]" % M] = (timeit(lambda i: ctx.softmax_ce_bwd_f32(P, P, Tg, capi.IDX_I32, 1.0, M, V, 0)), 2 * M * V * 4 + M * 4)
+        lossbuf = torch.empty(1, device="cuda")
+        out["softmax_ce_fwd [%d,32768]" % M] = (timeit(lambda i: ctx.softmax_ce_fwd_f32(lossbuf, P, P, Tg, capi.IDX_I32, M, V, 1e-5)), 2 * M * V * 4 + M * 4)
+        del P
     M, C = 16384, 1024
-    g, b, dg, db = torch.ones(C, device="cuda"), torch.zeros(C, device="cuda"), torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
-    sets = []
-    for _ in range(4):  # four disjoint (x, dy, dx, mean, rstd) sets, 201 MB each
-        x, dy = torch.randn(M, C, device="cuda"), torch.randn(M, C, device="cuda") * 1e-2
-        y, mu, rs, dx = torch.empty_like(x), torch.empty(M, device="cuda"), torch.empty(M, device="cuda"), torch.empty_like(x)
-        ctx.layernorm_fwd_f32(y, mu, rs, x, g, b, M, C, 1e-5)
-        sets.append((x, dy, dx, mu, rs))
-        del y
-    ln = lambda i: ctx.layernorm_bwd_f32(sets[i][2], dg, db, sets[i][1], sets[i][0], g, sets[i][3], sets[i][4], M, C, 0, 0)
-    ln_bytes = 3 * M * C * 4 + 2 * M * 4 + 3 * C * 4
-    out["layernorm_bwd [16384,1024]"] = (timeit(ln), ln_bytes)  # one isolated call per sample: the headline
-    out["layernorm_bwd [16384,1024] pipelined x4"] = (timeit(ln, calls=4), ln_bytes)
-    notes["layernorm_bwd [16384,1024] pipelined x4"] = "four back-to-back calls on four disjoint buffer sets per sample: launch latency hidden, as inside a training step"
-    rms = lambda i: ctx.rmsnorm_bwd_f32(sets[i][2], dg, sets[i][1], sets[i][0], g, sets[i][4], M, C, 0, 0)
-    out["rmsnorm_bwd [16384,1024]"] = (timeit(rms), 3 * M * C * 4 + M * 4 + 2 * C * 4)
-    del sets
+    if want("layernorm rmsnorm"):
+        g, b, dg, db = torch.ones(C, device="cuda"), torch.zeros(C, device="cuda"), torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
+        sets = []
+        for _ in range(4):  # four disjoint (x, dy, dx, mean, rstd) sets, 201 MB each
+            x, dy = torch.randn(M, C, device="cuda"), torch.randn(M, C, device="cuda") * 1e-2
+            y, mu, rs, dx = torch.empty_like(x), torch.empty(M, device="cuda"), torch.empty(M, device="cuda"), torch.empty_like(x)
+            ctx.layernorm_fwd_f32(y, mu, rs, x, g, b, M, C, 1e-5)
+            sets.append((x, dy, dx, mu, rs))
+            del y
+        ln = lambda i: ctx.layernorm_bwd_f32(sets[i][2], dg, db, sets[i][1], sets[i][0], g, sets[i][3], sets[i][4], M, C, 0, 0)
+        ln_bytes = 3 * M * C * 4 + 2 * M * 4 + 3 * C * 4
+        if want("layernorm"):
+            out["layernorm_bwd [16384,1024]"] = (timeit(ln), ln_bytes)  # one isolated call per sample: the headline
+            out["layernorm_bwd [16384,1024] pipelined x4"] = (timeit(ln, calls=4), ln_bytes)
+            notes["layernorm_bwd [16384,1024] pipelined x4"] = "four back-to-back calls on four disjoint buffer sets per sample: launch latency hidden, as inside a training step"
+        if want("rmsnorm"):
+            rms = lambda i: ctx.rmsnorm_bwd_f32(sets[i][2], dg, sets[i][1], sets[i][0], g, sets[i][4], M, C, 0, 0)
+            out["rmsnorm_bwd [16384,1024]"] = (timeit(rms), 3 * M * C * 4 + M * 4 + 2 * C * 4)
+        del sets
     M, F = 16384, 4096
-    x, dy = torch.randn(M, F, device="cuda"), torch.randn(M, F, device="cuda") * 1e-2
-    dx = torch.empty_like(x)
-    out["gelu_bwd [16384,4096]"] = (timeit(lambda i: ctx.gelu_bwd_f32(dx, dy, x, M * F, 0)), 3 * M * F * 4)
-    red = torch.empty(F, device="cuda")
-    out["reduce_rows (bias gradient) [16384,4096]"] = (timeit(lambda i: ctx.reduce_rows_f32(red, dy, M, F, 0)), M * F * 4 + F * 4)
-    del x, dy, dx
-    Bn, H, T = 16, 16, 1024
-    rows = Bn * H * T
-    S = torch.randn(rows, T, device="cuda")
-    tri = 4 * Bn * H * T * ((T + 1) // 2)  # bytes of one pass over the entries at or below the diagonal
-    out["causal_softmax_fwd [16,16,1024,1024]"] = (timeit(lambda i: ctx.causal_softmax_fwd_f32(S, S, 0.125, rows, T)), tri + 4 * rows * T)
-    dP = torch.randn(rows, T, device="cuda") * 1e-2
-    out["causal_softmax_bwd [16,16,1024,1024]"] = (timeit(lambda i: ctx.causal_softmax_bwd_f32(dP, dP, S, 0.125, rows, T, 0)), 2 * tri + 4 * rows * T)
-    del S, dP
-    n, Vv, Wd = 32768, 32768, 1024
-    idx_h = synth.zipf_tokens(4321, n, Vv).astype(np.int64)
-    idx = torch.from_numpy(idx_h).cuda()
-    dyv, table = torch.randn(n, Wd, device="cuda") * 1e-2, torch.zeros(Vv, Wd, device="cuda")
-    hit = int(np.unique(idx_h).size)
-    out["scatter_add [32768 Zipf(1.1) tokens, 32768 x 1024 table]"] = (timeit(lambda i: ctx.scatter_add_f32(table, idx, capi.IDX_I64, dyv, n, Wd, Vv)), n * Wd * 4 + 2 * hit * Wd * 4)
-    notes["scatter_add [32768 Zipf(1.1) tokens, 32768 x 1024 table]"] = "%d distinct rows hit; bytes = dy once + read-modify-write of the rows hit" % hit
-    del dyv, table
-    npar = 185759744
-    npar_pad = (npar + capi.ADAMW_CHUNK - 1) // capi.ADAMW_CHUNK * capi.ADAMW_CHUNK
-    w, m, v, gr = (torch.randn(npar_pad, device="cuda") * 0.02 for _ in range(4))
-    v.abs_()
-    mask = torch.ones(npar_pad // capi.ADAMW_CHUNK, dtype=torch.uint8, device="cuda")
-    out["adamw_arena [185.8 M parameters]"] = (timeit(lambda i: ctx.adamw_arena_f32(w, m, v, gr, mask, npar_pad, 3e-4, 0.9, 0.95, 0.9, 0.95, 0.1, 1e-5, 1.0)), 28 * npar_pad)
-    del w, m, v, gr
+    if want("gelu") or want("reduce_rows"):
+        x, dy = torch.randn(M, F, device="cuda"), torch.randn(M, F, device="cuda") * 1e-2
+        dx = torch.empty_like(x)
+        if want("gelu"):
+            out["gelu_bwd [16384,4096]"] = (timeit(lambda i: ctx.gelu_bwd_f32(dx, dy, x, M * F, 0)), 3 * M * F * 4)
+        if want("reduce_rows"):
+            red = torch.empty(F, device="cuda")
+            out["reduce_rows (bias gradient) [16384,4096]"] = (timeit(lambda i: ctx.reduce_rows_f32(red, dy, M, F, 0)), M * F * 4 + F * 4)
+        del x, dy, dx
+    if want("causal_softmax"):
+        Bn, H, T = 16, 16, 1024
+        rows = Bn * H * T
+        S = torch.randn(rows, T, device="cuda")
+        tri = 4 * Bn * H * T * ((T + 1) // 2)  # bytes of one pass over the entries at or below the diagonal
+        out["causal_softmax_fwd [16,16,1024,1024]"] = (timeit(lambda i: ctx.causal_softmax_fwd_f32(S, S, 0.125, rows, T)), tri + 4 * rows * T)
+        dP = torch.randn(rows, T, device="cuda") * 1e-2
+        out["causal_softmax_bwd [16,16,1024,1024]"] = (timeit(lambda i: ctx.causal_softmax_bwd_f32(dP, dP, S, 0.125, rows, T, 0)), 2 * tri + 4 * rows * T)
+        del S, dP
+    if want("scatter_add"):
+        n, Vv, Wd = 32768, 32768, 1024
+        idx_h = synth.zipf_tokens(4321, n, Vv).astype(np.int64)
+        idx = torch.from_numpy(idx_h).cuda()
+        dyv, table = torch.randn(n, Wd, device="cuda") * 1e-2, torch.zeros(Vv, Wd, device="cuda")
+        hit = int(np.unique(idx_h).size)
+        out["scatter_add [32768 Zipf(1.1) tokens, 32768 x 1024 table]"] = (timeit(lambda i: ctx.scatter_add_f32(table, idx, capi.IDX_I64, dyv, n, Wd, Vv)), n * Wd * 4 + 2 * hit * Wd * 4)
+        notes["scatter_add [32768 Zipf(1.1) tokens, 32768 x 1024 table]"] = "%d distinct rows hit; bytes = dy once + read-modify-write of the rows hit" % hit
+        del dyv, table
+    if want("adamw"):
+        npar = 185759744 // (8 if small else 1)
+        npar_pad = (npar + capi.ADAMW_CHUNK - 1) // capi.ADAMW_CHUNK * capi.ADAMW_CHUNK
+        w, m, v, gr = (torch.randn(npar_pad, device="cuda") * 0.02 for _ in range(4))
+        v.abs_()
+        mask = torch.ones(npar_pad // capi.ADAMW_CHUNK, dtype=torch.uint8, device="cuda")
+        out["adamw_arena [%.1f M parameters]" % (npar / 1e6)] = (timeit(lambda i: ctx.adamw_arena_f32(w, m, v, gr, mask, npar_pad, 3e-4, 0.9, 0.95, 0.9, 0.95, 0.1, 1e-5, 1.0)), 28 * npar_pad)
+        del w, m, v, gr
     ctx.sync()
     kernels = {k: {"ms": ms, "algorithmic_bytes": by, "achieved_gbs": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / pk["hbm_gbs"]} for k, (ms, by) in out.items()}
     for k, t in notes.items():
@@ -500,7 +513,9 @@ def kernel_suite(steps, warmup, device=0):
 
 def run_kernels(args):
     pk = peaks()
-    kernels = kernel_suite(args.steps, args.warmup)
+    kernels = kernel_suite(args.steps, args.warmup, only=args.only, small=args.small)
+    if not kernels:
+        raise SystemExit("bench.py: --only %r matches no kernel of the kernels workload" % args.only)
     worst = min(kernels.values(), key=lambda d: d["frac_of_hbm_peak"])
     print(json.dumps({"metric": "fused backward kernels, achieved HBM GB/s vs measured peak", "value": worst["frac_of_hbm_peak"], "unit": "fraction of HBM peak (worst kernel)", "n_gpus": 1,
                       "steps": max(5, args.steps), "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "f32", "data": "synthetic N(0,1) activations, N(0,1e-2) upstream gradients",
@@ -523,7 +538,7 @@ def run_gemm(args):
     shapes = [
         ("linear_fwd_NN_CxC", 0, 0, M, C, C, 1), ("linear_dX_NT_CxC", 0, 1, M, C, C, 1), ("linear_dW_TN_CxC_splitk", 1, 0, C, C, M, 1),
         ("fc1_fwd_NN_CxF", 0, 0, M, F, C, 1), ("fc2_dW_TN_FxC", 1, 0, F, C, M, 1), ("head_fwd_NT_CxV", 0, 1, M, V, C, 1), ("head_dE_TN_VxC", 1, 0, V, C, M, 1),
-        ("attn_scores_NT_batched", 0, 1, T, T, D, BH), ("attn_pv_NN_batched", 0, 0, T, D, T, BH), ("attn_dV_TN_batched", 1, 0, T, D, T, BH),
+        ("attn_scores_NT_batched", 0, 1, T, T, D, BH), ("attn_dS_NT_batched_softmax_bwd", 0, 1, T, T, D, BH), ("attn_pv_NN_batched", 0, 0, T, D, T, BH), ("attn_dV_TN_batched", 1, 0, T, D, T, BH),
     ]
     out = {}
     for name, opa, opb, m, n, k, nb in shapes:
@@ -534,6 +549,9 @@ def run_gemm(args):
             B = torch.randn((n, k) if opb else (k, n), device="cuda")
             Cm = torch.empty(m, n, device="cuda")
             fn = lambda: ctx.gemm_f32(opa, opb, m, n, k, 1.0, A, A.shape[1], B, B.shape[1], 0.0, Cm, n, None)
+            is_weight = "_fwd_" in name or "_dX_" in name  # B is a weight matrix there: registered for pre-split companions, as Module::to does
+            if is_weight:
+                ctx.weight_twins_register(B, B.shape[0], B.shape[1])
         else:
             Bn, H = 32, 16
             Cw = H * D
@@ -543,6 +561,10 @@ def run_gemm(args):
             O = torch.empty(Bn, T, Cw, device="cuda")
             if name.startswith("attn_scores"):
                 fn = lambda: ctx.gemm_batched_causal_f32(0, 1, T, T, D, 1.0, q, Cw, T * Cw, D, kk, Cw, T * Cw, D, 0.0, S, T, H * T * T, T * T, Bn, H, 1)
+            elif name.startswith("attn_dS"):
+                Pm = torch.rand(Bn * H, T, T, device="cuda").tril_()
+                rdot = torch.randn(Bn * H * T, device="cuda")
+                fn = lambda: ctx.gemm_batched_softmax_bwd_f32(0, 1, T, D, 1.0, q, Cw, T * Cw, D, kk, Cw, T * Cw, D, S, T, H * T * T, T * T, Bn, H, Pm, rdot, 0.125)
             elif name.startswith("attn_pv"):
                 fn = lambda: ctx.gemm_batched_causal_f32(0, 0, T, D, T, 1.0, S, T, H * T * T, T * T, kk, Cw, T * Cw, D, 0.0, O, Cw, T * Cw, D, Bn, H, 2)
             else:
@@ -559,6 +581,8 @@ def run_gemm(args):
             ts.append(s.elapsed_time(e))
         ms = float(np.median(ts))
         fl = 2.0 * m * n * k * nb
+        if nb == 1 and is_weight:
+            ctx.weight_twins_drop(B, B.numel() * 4)
         out[name] = {"ms": ms, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / pk["tensor_tflops_burst"], "frac_of_split_ceiling": fl / ms / 1e9 / (pk["tensor_tflops_burst"] / units), "engine": ctx.ctx_last_gemm_engine()}
         del fn
     ctx.sync()
@@ -581,7 +605,8 @@ def main():
     ap.add_argument("--no-kernels", action="store_true", help="skip the fused-kernel microbenchmarks of the default line")
     ap.add_argument("--no-reference-cuda", action="store_true", help="skip the reference-CUDA leg of the default line")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
-    ap.add_argument("--only", default="", help="gemm workload: run only the shapes whose name contains this text")
+    ap.add_argument("--only", default="", help="gemm / kernels workloads: run only the entries whose name contains this text")
+    ap.add_argument("--small", action="store_true", help="kernels workload: an eighth of the loss rows / optimizer parameters (profiler captures)")
     args = ap.parse_args()
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference-cuda":
