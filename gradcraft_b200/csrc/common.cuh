@@ -96,6 +96,9 @@ struct gcb_ctx {
     std::unordered_map<const float*, int> twin_index;
     const char *twins_lo = nullptr, *twins_hi = nullptr;  // address range covering every registered weight
     bool twins_dirty = false;
+    void* twin_jobs = nullptr;       // device table of the pre-split jobs (one launch recomputes every companion)
+    int64_t twin_jobs_total = 0;
+    bool twin_jobs_stale = true;
     std::mutex mu;
 };
 

@@ -25,46 +25,75 @@ __device__ __forceinline__ uint32_t tw_pack_bf16(float lo, float hi) {
 }
 __device__ __forceinline__ float tw_trunc_tf32(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 
-// One thread per 16-byte chunk (8 consecutive k of one n) of one orientation.
+// One job per (weight, orientation); all jobs of a context run in one launch.
+struct TwinJob {
+    const float* W;
+    uint4* out;
+    int64_t N, K, ld;
+    int64_t first;  // index of this job's first 16-byte chunk among all jobs' chunks
+    int kn;
+};
+
+// One thread per 16-byte chunk (8 consecutive k of one n) of one job.
 // out layout (bf16): [which = big, small][n_group = ceil(N / 8)][k_chunk = Kp / 8][n % 8][k % 8], Kp = K rounded up to 16.
 // kn != 0: W is stored K x N (element (k, n) at W[k * ld + n]); kn == 0: stored N x K (element (k, n) at W[n * ld + k]).
-__global__ void __launch_bounds__(256) presplit_kernel(uint4* __restrict__ out, const float* __restrict__ W, int64_t N, int64_t K, int64_t ld, int kn) {
-    const int64_t n_groups = (N + 7) / 8, k_chunks = ((K + 15) / 16) * 2;
-    const int64_t total = n_groups * 8 * k_chunks;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+__global__ void __launch_bounds__(256) presplit_kernel(const TwinJob* __restrict__ jobs, int n_jobs, int64_t total) {
+    for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
+        int lo = 0, hi = n_jobs;  // last job with first <= g
+        while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (jobs[mid].first <= g) lo = mid; else hi = mid; }
+        const TwinJob j = jobs[lo];
+        const int64_t i = g - j.first;
+        const int64_t n_groups = (j.N + 7) / 8, k_chunks = ((j.K + 15) / 16) * 2;
         // thread order: n fastest for the K x N storage (coalesced along n), k chunk fastest for the N x K storage (coalesced along k)
         int64_t n, kc;
-        if (kn) { n = i % (n_groups * 8); kc = i / (n_groups * 8); }
+        if (j.kn) { n = i % (n_groups * 8); kc = i / (n_groups * 8); }
         else { kc = i % k_chunks; n = i / k_chunks; }
         float x[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const int64_t k = kc * 8 + e;
-            x[e] = (n < N && k < K) ? (kn ? W[k * ld + n] : W[n * ld + k]) : 0.0f;
+            x[e] = (n < j.N && k < j.K) ? (j.kn ? j.W[k * j.ld + n] : j.W[n * j.ld + k]) : 0.0f;
         }
         float s[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) s[e] = x[e] - tw_trunc_tf32(x[e]);
         const int64_t slot = ((n >> 3) * k_chunks + kc) * 8 + (n & 7);  // in 16-byte units
-        out[slot] = make_uint4(tw_pack_bf16(x[0], x[1]), tw_pack_bf16(x[2], x[3]), tw_pack_bf16(x[4], x[5]), tw_pack_bf16(x[6], x[7]));
-        out[n_groups * k_chunks * 8 + slot] = make_uint4(tw_pack_bf16(s[0], s[1]), tw_pack_bf16(s[2], s[3]), tw_pack_bf16(s[4], s[5]), tw_pack_bf16(s[6], s[7]));
+        j.out[slot] = make_uint4(tw_pack_bf16(x[0], x[1]), tw_pack_bf16(x[2], x[3]), tw_pack_bf16(x[4], x[5]), tw_pack_bf16(x[6], x[7]));
+        j.out[n_groups * k_chunks * 8 + slot] = make_uint4(tw_pack_bf16(s[0], s[1]), tw_pack_bf16(s[2], s[3]), tw_pack_bf16(s[4], s[5]), tw_pack_bf16(s[6], s[7]));
     }
 }
 
 size_t twin_bytes(int64_t N, int64_t K) { return (size_t)2 * ((N + 7) / 8) * (((K + 15) / 16) * 2) * 128; }
 
+// Recomputes the companions of every registered weight: one launch over a job table kept in device memory (rebuilt when the
+// set of registered weights changed).
 int twins_refresh(gcb_ctx* ctx) {
     cudaSetDevice(ctx->device);
-    for (auto& t : ctx->twins) {
-        // stored rows x cols: as a K x N operand K = rows, N = cols; as an N x K operand N = rows, K = cols
-        const int64_t tot_kn = ((t.cols + 7) / 8) * 8 * (((t.rows + 15) / 16) * 2), tot_nk = ((t.rows + 7) / 8) * 8 * (((t.cols + 15) / 16) * 2);
-        presplit_kernel<<<(unsigned)std::min<int64_t>((tot_kn + 255) / 256, (int64_t)kSMs * 16), 256, 0, ctx->stream>>>((uint4*)t.kn, t.base, t.cols, t.rows, t.cols, 1);
-        int rc = after_launch(ctx, "presplit_weight");
+    if (ctx->twins.empty()) { ctx->twins_dirty = false; return GCB_OK; }
+    const int n_jobs = 2 * (int)ctx->twins.size();
+    if (ctx->twin_jobs_stale || ctx->twin_jobs == nullptr) {
+        std::vector<TwinJob> jobs;
+        int64_t total = 0;
+        for (auto& t : ctx->twins) {
+            // stored rows x cols: as a K x N operand K = rows, N = cols; as an N x K operand N = rows, K = cols
+            jobs.push_back({t.base, (uint4*)t.kn, t.cols, t.rows, t.cols, total, 1});
+            total += ((t.cols + 7) / 8) * 8 * (((t.rows + 15) / 16) * 2);
+            jobs.push_back({t.base, (uint4*)t.nk, t.rows, t.cols, t.cols, total, 0});
+            total += ((t.rows + 7) / 8) * 8 * (((t.cols + 15) / 16) * 2);
+        }
+        if (ctx->twin_jobs) ctx->arena.free(ctx->twin_jobs);
+        ctx->twin_jobs = nullptr;
+        int rc = ctx->arena.alloc(sizeof(TwinJob) * jobs.size(), &ctx->twin_jobs);
         if (rc) return rc;
-        presplit_kernel<<<(unsigned)std::min<int64_t>((tot_nk + 255) / 256, (int64_t)kSMs * 16), 256, 0, ctx->stream>>>((uint4*)t.nk, t.base, t.rows, t.cols, t.cols, 0);
-        rc = after_launch(ctx, "presplit_weight");
-        if (rc) return rc;
+        // the table is tiny and changes only when weights are registered or dropped: a synchronous copy keeps the host vector's lifetime simple
+        GCB_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+        GCB_CHECK_CUDA(cudaMemcpy(ctx->twin_jobs, jobs.data(), sizeof(TwinJob) * jobs.size(), cudaMemcpyHostToDevice));
+        ctx->twin_jobs_total = total;
+        ctx->twin_jobs_stale = false;
     }
+    presplit_kernel<<<(unsigned)std::min<int64_t>((ctx->twin_jobs_total + 255) / 256, (int64_t)kSMs * 16), 256, 0, ctx->stream>>>((const TwinJob*)ctx->twin_jobs, n_jobs, ctx->twin_jobs_total);
+    int rc = after_launch(ctx, "presplit_weight");
+    if (rc) return rc;
     ctx->twins_dirty = false;
     return GCB_OK;
 }
@@ -108,6 +137,7 @@ int gcb_weight_twins_register(gcb_ctx* ctx, const float* W, int64_t rows, int64_
     if (ctx->twins.size() == 1 || lo < ctx->twins_lo) ctx->twins_lo = lo;
     if (ctx->twins.size() == 1 || hi > ctx->twins_hi) ctx->twins_hi = hi;
     ctx->twins_dirty = true;
+    ctx->twin_jobs_stale = true;
     return GCB_OK;
 }
 
@@ -122,6 +152,8 @@ int gcb_weight_twins_drop(gcb_ctx* ctx, const void* range_begin, size_t bytes) {
         else keep.push_back(t);
     }
     ctx->twins.swap(keep);
+    ctx->twin_jobs_stale = true;
+    if (ctx->twins.empty() && ctx->twin_jobs) { ctx->arena.free(ctx->twin_jobs); ctx->twin_jobs = nullptr; }
     ctx->twin_index.clear();
     ctx->twins_lo = ctx->twins_hi = nullptr;
     for (size_t i = 0; i < ctx->twins.size(); ++i) {
