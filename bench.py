@@ -204,8 +204,8 @@ def run_reference_arm(args, rank):
     arch, V, T, C, H, L, F, B, accum = WORKLOADS[args.workload]
     t0 = time.time()
     Ts = min(T, CPU_SAMPLE_T or T)
-    est_s = 16.0 * (flops_per_token(V, Ts, C, L, F) * Ts) / (flops_per_token(32768, 1024, 1024, 12, 4096) * 1024)  # ~16 s per full-sequence step for gpt180m on 16 cores
-    fit = max(2, int(240.0 / max(est_s, 1e-3)))
+    est_s = 18.7 * (flops_per_token(V, Ts, C, L, F) * Ts) / (flops_per_token(32768, 1024, 1024, 12, 4096) * 1024)  # ~18.7 s per full-sequence step (with clip) for gpt180m on 16 cores
+    fit = max(2, int(190.0 / max(est_s, 1e-3)))
     warm = min(args.warmup, max(1, fit // 5))
     steps = max(1, min(args.steps, fit - warm))
     tok_s, cores, desc, kind, ms_step = reference_cpu_run(args.workload, steps, warm)
@@ -461,6 +461,9 @@ def kernel_suite(steps, warmup, device=0, only="", small=False):
             out["layernorm_bwd [16384,1024]"] = (timeit(ln), ln_bytes)  # one isolated call per sample: the headline
             out["layernorm_bwd [16384,1024] pipelined x4"] = (timeit(ln, calls=4), ln_bytes)
             notes["layernorm_bwd [16384,1024] pipelined x4"] = "four back-to-back calls on four disjoint buffer sets per sample: launch latency hidden, as inside a training step"
+            lna = lambda i: ctx.layernorm_bwd_f32(sets[i][2], dg, db, sets[i][1], sets[i][0], g, sets[i][3], sets[i][4], M, C, 1, 1)
+            out["layernorm_bwd accumulating into dx [16384,1024] pipelined x4"] = (timeit(lna, calls=4), ln_bytes + M * C * 4)
+            notes["layernorm_bwd accumulating into dx [16384,1024] pipelined x4"] = "the form the residual stream's gradient takes in the step: dx is read, added to and written back (four arrays of traffic)"
         if want("rmsnorm"):
             rms = lambda i: ctx.rmsnorm_bwd_f32(sets[i][2], dg, sets[i][1], sets[i][0], g, sets[i][4], M, C, 0, 0)
             out["rmsnorm_bwd [16384,1024]"] = (timeit(rms), 3 * M * C * 4 + M * 4 + 2 * C * 4)

@@ -221,6 +221,16 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) norm_bwd_ring(float* __res
         if (!__all_sync(0xffffffffu, ring_wait(my_bar0 + 8u * s, parity, status))) break;
         const float* xs = my_ring + (size_t)s * 2 * cols;
         const float* ds = xs + cols;
+        // accumulating into an existing dx (the residual stream's gradient): its old values are requested now, so that their
+        // global-memory latency passes behind the statistics pass instead of stalling the store loop
+        float4 old[NCHUNK];
+        if (dx != nullptr && acc_dx) {
+#pragma unroll
+            for (int k = 0; k < NCHUNK; ++k) {
+                const int c = (lane + 32 * k) * 4;
+                old[k] = (c < cols) ? ld4_stream(dx + r * cols + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
         float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
         for (int k = 0; k < NCHUNK; ++k) {
@@ -247,7 +257,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) norm_bwd_ring(float* __res
                     const float4 xv = ld4(xs + c), dv = ld4(ds + c), g = ld4(sgamma + c);
                     float4 o = make_float4(rs * (dv.x * g.x - m1 - (xv.x - mu) * rs * m2), rs * (dv.y * g.y - m1 - (xv.y - mu) * rs * m2), rs * (dv.z * g.z - m1 - (xv.z - mu) * rs * m2),
                                            rs * (dv.w * g.w - m1 - (xv.w - mu) * rs * m2));
-                    if (acc_dx) { const float4 old = ld4(or_ + c); o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+                    if (acc_dx) { o.x += old[k].x; o.y += old[k].y; o.z += old[k].z; o.w += old[k].w; }
                     st4_stream(or_ + c, o);
                 }
             }

@@ -34,6 +34,7 @@ def rnd(seed, *shape):
     (0, 1, 128, 64, 64), (0, 0, 128, 256, 32), (1, 0, 128, 128, 48), (1, 1, 128, 128, 16),
     (0, 0, 300, 520, 100), (0, 1, 257, 1000, 132), (1, 0, 200, 72, 1028), (1, 1, 132, 260, 36),
     (0, 0, 1024, 1024, 1024), (1, 0, 512, 512, 8192),
+    (0, 0, 300, 64, 1000), (1, 0, 260, 48, 520), (0, 1, 640, 64, 4096), (1, 1, 384, 36, 272),  # 64-wide tiles with long K loops, ragged edges
 ])
 def test_tc_gemm_vs_numpy(env, opa, opb, M, N, K):
     ctx, torch, capi = env
