@@ -211,16 +211,18 @@ __device__ __forceinline__ void split_hybrid(const uint8_t* raw, uint8_t* twin, 
     uint8_t* sml = twin + ROWS * 32;
     if (!MN) {
         // raw: ROWS rows of 64 B (16 k), 16-byte chunk index XOR ((row >> 1) & 3)  [64-byte swizzle]
-        float4 x[ROWS / 32];
+        // A thread takes one half row (8 k = two chunks) and writes it as one 16-byte core-matrix row of each companion.  Eight
+        // consecutive lanes take eight consecutive rows of the same half: their loads fall into the eight different 16-byte
+        // slots of a 128-byte bank line (that is what the swizzle is for) and so do their stores: no bank conflicts either way.
 #pragma unroll
-        for (int v = 0; v < ROWS / 32; ++v) x[v] = reinterpret_cast<const float4*>(raw)[t + 128 * v];
-#pragma unroll
-        for (int v = 0; v < ROWS / 32; ++v) {
-            const int idx = t + 128 * v, row = idx >> 2, lc = (idx & 3) ^ ((row >> 1) & 3);  // lc: logical chunk = k / 4
-            const uint32_t off = (uint32_t)(row >> 3) * 256u + (uint32_t)(lc >> 1) * 128u + (uint32_t)(row & 7) * 16u + (uint32_t)(lc & 1) * 8u;
-            const float4 s = make_float4(x[v].x - trunc_tf32(x[v].x), x[v].y - trunc_tf32(x[v].y), x[v].z - trunc_tf32(x[v].z), x[v].w - trunc_tf32(x[v].w));
-            *reinterpret_cast<uint2*>(big + off) = make_uint2(pack_bf16(x[v].x, x[v].y), pack_bf16(x[v].z, x[v].w));
-            *reinterpret_cast<uint2*>(sml + off) = make_uint2(pack_bf16(s.x, s.y), pack_bf16(s.z, s.w));
+        for (int v = 0; v < ROWS / 64; ++v) {
+            const int u = t + 128 * v, q = u >> 3, h = q & 1, row = (q >> 1) * 8 + (u & 7), sw = (row >> 1) & 3;
+            const uint8_t* r = raw + row * 64;
+            const float4 a = *reinterpret_cast<const float4*>(r + (((2 * h) ^ sw) << 4)), b = *reinterpret_cast<const float4*>(r + (((2 * h + 1) ^ sw) << 4));
+            const uint32_t off = (uint32_t)(row >> 3) * 256u + (uint32_t)h * 128u + (uint32_t)(row & 7) * 16u;
+            *reinterpret_cast<uint4*>(big + off) = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+            *reinterpret_cast<uint4*>(sml + off) = make_uint4(pack_bf16(a.x - trunc_tf32(a.x), a.y - trunc_tf32(a.y)), pack_bf16(a.z - trunc_tf32(a.z), a.w - trunc_tf32(a.w)),
+                                                              pack_bf16(b.x - trunc_tf32(b.x), b.y - trunc_tf32(b.y)), pack_bf16(b.z - trunc_tf32(b.z), b.w - trunc_tf32(b.w)));
         }
     } else {
         // raw: ROWS / 32 boxes of 16 k-rows x 32 floats (128 B rows), 32-byte unit index XOR (k & 3)  [128-byte swizzle in 32-byte units]
