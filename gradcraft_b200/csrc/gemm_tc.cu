@@ -7,7 +7,7 @@
 //   warp 1      MMA issuer: allocates 2 x BN TMEM columns (double-buffered accumulator), issues the tcgen05.mma sequence
 //   warps 2..5  splitter: derives the second-order parts of every landed tile into its twin tile
 //   warps 6..9  epilogue: TMEM -> registers -> smem transpose -> 128-byte row segments in global memory, overlapped with
-//               the main loop of the next tile
+//               the main loop of the next tile (the 256-wide kernel: eight warps, TMEM -> swizzled smem blocks -> TMA stores)
 // Split operands: every fp32 value is x = t + s, t = x truncated to TF32 (the tensor core reads t straight from the raw
 // tile: it ignores the 13 low mantissa bits) and s = x - t, exact.  The default mode accumulates
 //   t_a t_b (kind::tf32)  +  bf16(s_a) bf16(b)  +  bf16(a) bf16(s_b) (kind::f16, BF16 inputs, twice the TF32 rate)
@@ -23,6 +23,8 @@
 // (TMEM is always released), so a logic error cannot hang the device.
 // Split-K (deterministic): when a problem has too few tiles to fill 148 SMs, K is cut into slices whose partial tiles go
 // to scratch memory and are summed in slice order by a second kernel.
+// By-products and shortcuts of the CTA-pair kernel: a registered weight's BF16 companions arrive pre-split by TMA (twins.cu),
+// and the column sums of op(B) — the bias gradient beside dW = X^T dY — are gathered by the B-splitter warps.
 #include <cuda.h>
 
 #include "gemm.cuh"

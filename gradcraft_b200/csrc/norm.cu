@@ -7,7 +7,8 @@
 // x / dy are read exactly once.  In the backward the warp also keeps its gamma and its running dgamma / dbeta
 // column sums in registers across all the rows it visits; the per-warp sums are combined through shared memory
 // into one partial per CTA and a second tiny kernel adds the CTA partials in a fixed order (no atomics, so the
-// result is deterministic).  Other shapes take a CTA-per-row kernel with the same arithmetic.
+// result is deterministic).  Inputs of 4736 rows or more take a persistent kernel that stages rows through shared
+// memory with bulk async copies instead; other shapes a CTA-per-row kernel with the same arithmetic.
 #include <atomic>
 
 #include "common.cuh"
@@ -286,35 +287,29 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) norm_bwd_ring(float* __res
     }
 }
 
-// Second stage of dgamma / dbeta: sums the per-CTA partial rows in a fixed order.  A block covers 32 of the 2 * cols
-// outputs; its 8 thread groups take the partial rows k = g, g + 8, ... (four independent accumulators each, so the loads
-// overlap), and the 8 group sums are added in group order.
+// Second stage of dgamma / dbeta: sums the per-CTA partial rows in a fixed order.  One warp per output column: lane l
+// loads the partial rows l, l + 32, ... (all loads of a lane are independent, so the stage is one L2 round trip deep),
+// adds its own in ascending row order, and the 32 lane sums are combined by a shuffle tree — the same tree for every
+// launch, so the result is deterministic.
 __global__ void __launch_bounds__(256) norm_params_stage2(float* __restrict__ dgamma, float* __restrict__ dbeta, const float* __restrict__ partial, int nparts, int cols, int accumulate) {
-    __shared__ float red[8][33];
-    const int lane_c = threadIdx.x & 31, g = threadIdx.x >> 5;
-    const int i = blockIdx.x * 32 + lane_c;  // over 2 * cols
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * 8 + (threadIdx.x >> 5);  // over 2 * cols
     // launched with programmatic stream serialisation: this grid may start while the kernel that writes `partial` drains;
     // nothing of it is read before that kernel has completed and its writes are visible
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-    if (i < 2 * cols) {
-        const float* p = partial + i;
-        const size_t stride = (size_t)2 * cols;
-        int k = g;
-        for (; k + 24 < nparts; k += 32) {
-            a0 += p[(size_t)k * stride];
-            a1 += p[(size_t)(k + 8) * stride];
-            a2 += p[(size_t)(k + 16) * stride];
-            a3 += p[(size_t)(k + 24) * stride];
-        }
-        for (; k < nparts; k += 8) a0 += p[(size_t)k * stride];
-    }
-    red[g][lane_c] = (a0 + a1) + (a2 + a3);
-    __syncthreads();
-    if (g == 0 && i < 2 * cols) {
-        float s = 0.0f;
+    if (i >= 2 * cols) return;
+    const float* p = partial + i;
+    const size_t stride = (size_t)2 * cols;
+    float v[8];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) s += red[q][lane_c];
+    for (int u = 0; u < 8; ++u) {
+        const int k = lane + 32 * u;
+        v[u] = k < nparts ? __ldcg(p + (size_t)k * stride) : 0.0f;
+    }
+    float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+    for (int k = lane + 256; k < nparts; k += 32) s += __ldcg(p + (size_t)k * stride);  // more than 256 partial rows: the rest in order
+    s = warp_sum(s);
+    if (lane == 0) {
         float* dst = (i < cols) ? dgamma : dbeta;
         if (dst != nullptr) {
             const int c = (i < cols) ? i : i - cols;
@@ -327,7 +322,7 @@ __global__ void __launch_bounds__(256) norm_params_stage2(float* __restrict__ dg
 // two dependent launches is a tenth of this backward at 16k x 1k).
 static cudaError_t launch_params_stage2(cudaStream_t stream, float* dgamma, float* dbeta, const float* partial, int nparts, int cols, int accumulate) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((2 * cols + 31) / 32), 1, 1);
+    cfg.gridDim = dim3((unsigned)((2 * cols + 7) / 8), 1, 1);
     cfg.blockDim = dim3(256, 1, 1);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -71,7 +71,7 @@ GCB_API int gcb_selftest_bounded_wait(gcb_ctx* ctx, int max_polls);
 GCB_API int64_t gcb_ctx_launch_count(gcb_ctx* ctx);
 /* Launches whose kernel-family name starts with `prefix` (for tests and benches that assert which code path ran).  Families:
  * gemm_tc_pair[_gelu_fwd|_gelu_bwd], gemm_tc_256[_softmax_bwd], gemm_tc_128, gemm_tc_64, splitk_reduce, gemm_simt,
- * layernorm_bwd_ring, layernorm_bwd_warp, rmsnorm_bwd_ring, ..., one per entry point otherwise. */
+ * presplit_weight, layernorm_bwd_ring, layernorm_bwd_warp, rmsnorm_bwd_ring, ..., one per entry point otherwise. */
 GCB_API int64_t gcb_ctx_launch_count_named(gcb_ctx* ctx, const char* prefix);
 /* Which GEMM engine ran last: 0 none, 1 SIMT fp32, 2 tcgen05 (split fp32). */
 GCB_API int gcb_ctx_last_gemm_engine(gcb_ctx* ctx);
