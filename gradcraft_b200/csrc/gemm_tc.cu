@@ -404,6 +404,7 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot_gen;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a split-K reduction behind this grid may be scheduled while it drains; it still waits for the grid to complete
 
     if (warp == 0) {
         // ---------------- producer ----------------
@@ -891,6 +892,7 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     cluster_sync_all();  // both CTAs' barriers are initialised before anyone arrives on a remote one
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a split-K reduction behind this grid may be scheduled while it drains; it still waits for the grid to complete
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot_gen;
 
@@ -966,6 +968,9 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                             umma_tf32_pair_ts(d_tmem, a0 + 8 * j, B_MN ? make_desc(sb + b_off, 2048, 512, 1) : make_desc(sb + b_off, 16, 512, 4), idesc & ~(1u << 15), (i | j) ? 1u : 0u);
                         }
                         umma_bf16_pair_ts(d_tmem, a0 + 24, make_desc(tb, 128, 256, 0), idesc_bf, 1u);
+#ifdef GCB_TC_TRACE
+                        if (!(p.dbg & 16))
+#endif
                         umma_bf16_pair_ts(d_tmem, a0 + 16, make_desc(tb + S::B_BYTES / 2, 128, 256, 0), idesc_bf, 1u);
                     } else {
 #pragma unroll
@@ -1168,18 +1173,42 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
     }
 }
 
-// C = alpha * sum_s partial[s] + beta * C + bias, slices added in ascending order
+// C = alpha * sum_s partial[s] + beta * C + bias, slices added in ascending order.  Launched with programmatic stream
+// serialisation behind the GEMM that wrote the partial tiles: its blocks may be scheduled while that grid drains, and
+// nothing is read before the grid has completed.  `vec` = every row of C and of the partial tiles starts on a 16-byte
+// boundary and N % 4 == 0 (four columns per thread, same order of additions per element as the scalar form).
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(float* __restrict__ C, const float* __restrict__ partial, const float* __restrict__ bias, int64_t M, int64_t N, int64_t ldc, int splits,
-                                                            float alpha, float beta, float* __restrict__ colsum, const float* __restrict__ colsum_partial, int colsum_accumulate) {
+                                                            float alpha, float beta, float* __restrict__ colsum, const float* __restrict__ colsum_partial, int colsum_accumulate, int vec) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t total = M * N;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (int64_t)gridDim.x * blockDim.x;
     if (colsum != nullptr) {  // the column sums of op(B), one partial per K slice
-        for (int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; n < N; n += (int64_t)gridDim.x * blockDim.x) {
+        for (int64_t n = tid; n < N; n += nthreads) {
             float s = 0.0f;
             for (int k = 0; k < splits; ++k) s += colsum_partial[(int64_t)k * N + n];
             colsum[n] = colsum_accumulate ? colsum[n] + s : s;
         }
     }
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    if (vec) {
+        const int64_t n4 = N >> 2, total4 = total >> 2;
+        for (int64_t i = tid; i < total4; i += nthreads) {
+            const int64_t m = i / n4, n = (i - m * n4) << 2;
+            const float4* src = reinterpret_cast<const float4*>(partial) + i;
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+            for (int k = 0; k < splits; ++k) {
+                const float4 v = __ldcg(src + (int64_t)k * total4);
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
+            float4 o = make_float4(alpha * s.x, alpha * s.y, alpha * s.z, alpha * s.w);
+            if (bias) { o.x += bias[n]; o.y += bias[n + 1]; o.z += bias[n + 2]; o.w += bias[n + 3]; }
+            float4* dst = reinterpret_cast<float4*>(C + m * ldc + n);
+            if (beta != 0.0f) { const float4 old = *dst; o.x += beta * old.x; o.y += beta * old.y; o.z += beta * old.z; o.w += beta * old.w; }
+            *dst = o;
+        }
+        return;
+    }
+    for (int64_t i = tid; i < total; i += nthreads) {
         const int64_t m = i / N, n = i - m * N;
         float s = 0.0f;
         for (int k = 0; k < splits; ++k) s += partial[(int64_t)k * total + i];
@@ -1440,8 +1469,19 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     if (rc) return rc;
     if (splits > 1) {
         const int64_t total = g.M * g.N;
-        splitk_reduce_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)kSMs * 8), 256, 0, ctx->stream>>>(g.C, p.partial, g.bias, g.M, g.N, g.ldc, splits, g.alpha, g.beta, g.colsum,
-                                                                                                                              p.colsum_partial, g.colsum_accumulate);
+        const int vec = (g.N % 4 == 0 && g.ldc % 4 == 0 && aligned16(g.C) && aligned16(p.partial)) ? 1 : 0;
+        const int64_t units = vec ? total / 4 : total;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)std::min<int64_t>((units + 255) / 256, (int64_t)kSMs * 8), 1, 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        GCB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, g.C, (const float*)p.partial, g.bias, g.M, g.N, g.ldc, splits, g.alpha, g.beta, g.colsum, (const float*)p.colsum_partial,
+                                          g.colsum_accumulate, vec));
         rc = after_launch(ctx, "splitk_reduce");
         if (rc) return rc;
     }
