@@ -75,7 +75,7 @@ def test_mid_size_training_step_runs_the_full_size_kernels_and_matches_reference
     attention GEMMs and the staged LayerNorm backward, i.e. the kernels the full-size benchmark runs, and is held to the
     same loss / gradient / weight bar against the compiled reference (3 steps with clipping)."""
     run_case("mid_lngelu", families=("gemm_tc_pair", "gemm_tc_pair_gelu_fwd", "gemm_tc_pair_gelu_bwd", "splitk_reduce", "gemm_tc_256_softmax_bwd", "gemm_tc_64",
-                                     "layernorm_bwd_ring", "adamw_arena", "scatter_accumulate", "softmax_ce_bwd"))
+                                     "layernorm_bwd_ring", "adamw_arena", "scatter_accumulate", "scatter_fold", "softmax_ce_bwd"))
 
 
 def test_training_matches_reference_with_three_tf32_products():
