@@ -78,6 +78,13 @@ def test_mid_size_training_step_runs_the_full_size_kernels_and_matches_reference
                                      "layernorm_bwd_ring", "adamw_arena", "scatter_accumulate", "scatter_fold", "softmax_ce_bwd"))
 
 
+def test_mid_size_rmsnorm_swiglu_training_step_matches_reference():
+    """The reference's own GPT (RMSNorm + SwiGLU) at 5120 rows: the staged RMSNorm backward, the fused SwiGLU kernels and the
+    CTA-pair GEMM on 768-wide outputs, held to the loss / gradient / weight bar against the compiled reference (3 steps, clip)."""
+    run_case("mid_rmsswiglu", families=("gemm_tc_pair", "splitk_reduce", "gemm_tc_256_softmax_bwd", "gemm_tc_64", "rmsnorm_bwd_ring", "swiglu_fwd", "swiglu_bwd", "adamw_arena",
+                                        "scatter_accumulate", "scatter_fold", "softmax_ce_bwd"))
+
+
 def test_training_matches_reference_with_three_tf32_products():
     """The same parity bar with the GEMM engine in split mode 1 (classic 3xTF32) instead of the default TF32 + 2 x BF16."""
     run_case("config1_lngelu", split_mode=1)
