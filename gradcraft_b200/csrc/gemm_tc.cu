@@ -285,7 +285,7 @@ struct RoleTrace {
 // shared-memory traffic of a narrow tile — the resource these kernels run out of first.
 template <int BN, bool A_TM = false>
 struct TcSmem {
-    static constexpr int STAGES = A_TM ? (BN == 64 ? 4 : 8) : (BN == 128 ? 4 : 3);  // narrow tiles: two CTAs per SM (two issuer / producer threads) beat one deeper ring (measured)
+    static constexpr int STAGES = A_TM ? (BN == 64 ? 5 : 8) : (BN == 128 ? 4 : 3);  // narrow tiles: two CTAs per SM (two issuer / producer threads) beat one deeper ring (measured)
     // 256-wide tiles are used for short K loops (attention scores / dS): their epilogue is the bottleneck, so eight warps
     // share it, two per TMEM lane quarter with half of the columns each
     static constexpr int EPI_WARPS = BN == 256 ? 8 : 4;
@@ -294,8 +294,11 @@ struct TcSmem {
     static constexpr int B_BYTES = BN * TC_BK * 4;
     static constexpr int B_OFF = A_TM ? A_BYTES : 2 * A_BYTES;     // raw A [+ its twin], then raw B + its twin
     static constexpr int STAGE_BYTES = B_OFF + 2 * B_BYTES;
-    static constexpr int TMEM_COLS = A_TM ? (BN == 64 ? 256 : 512) : 2 * BN;  // two accumulators [+ STAGES x 32 columns of A]
-    static constexpr int A_TMEM_COL0 = 2 * BN;
+    // the 64-wide tiles (long K loops over a streamed A operand, two CTAs per SM) keep ONE accumulator and spend the columns on a
+    // fifth A stage: what bounds them is the A bytes in flight, and their epilogue is 1 / 64 of a tile's time
+    static constexpr int NACC = (A_TM && BN == 64) ? 1 : 2;
+    static constexpr int TMEM_COLS = A_TM ? (BN == 64 ? 256 : 512) : 2 * BN;  // accumulators [+ STAGES x 32 columns of A]
+    static constexpr int A_TMEM_COL0 = NACC * BN;
     static_assert(!A_TM || (BN <= 128 && A_TMEM_COL0 + STAGES * 32 <= TMEM_COLS), "A stages do not fit beside the accumulators");
     static constexpr int EPI_PITCH = 36;                           // floats per staged row: 32 + 4 keeps float4 alignment and spreads banks
     // one 32 x 32 transposition buffer per epilogue warp; the 256-wide kernel instead keeps two 4 KB blocks per warp in the
@@ -455,8 +458,8 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
             for (int64_t w = blockIdx.x; w < p.loop_end && ok; w += gridDim.x) {
                 const TileCoord tc = tile_coord(p, w, BN);
                 if (tc.skip) continue;
-                const uint32_t buf = lt & 1u;
-                ok = mbar_wait(acc_empty_bar(buf), ((lt >> 1) & 1u) ^ 1u, p.status, 5);  // the epilogue has drained this accumulator
+                const uint32_t buf = lt % S::NACC;
+                ok = mbar_wait(acc_empty_bar(buf), ((lt / S::NACC) & 1u) ^ 1u, p.status, 5);  // the epilogue has drained this accumulator
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + buf * BN;
@@ -584,7 +587,7 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
             for (int64_t w = blockIdx.x; w < p.loop_end && ok; w += gridDim.x) {
                 const TileCoord tc = tile_coord(p, w, BN);
                 if (tc.skip) continue;
-                const uint32_t buf = lt & 1u;
+                const uint32_t buf = lt % S::NACC;
                 const int64_t n_end = p.causal == 1 ? min(p.N, (int64_t)tc.m0 + TC_BM) : p.N;
                 const int64_t col0 = (int64_t)tc.n0 + 32 * c_begin;
                 const int nchunks = (int)max((int64_t)0, min((int64_t)4, (n_end - col0 + 31) / 32));
@@ -598,7 +601,7 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
                         tma_load_4d(blk_sh + (nblk & 1) * 4096, &map_p, probs_bar(ew, nblk & 1), (int)col0, m_blk, tc.b_in, tc.b_out);
                     }
                 }
-                ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0);
+                ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt / S::NACC) & 1u, p.status, 4)) != 0);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -680,7 +683,7 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
         for (int64_t w = blockIdx.x; w < p.loop_end && ok; w += gridDim.x) {
             const TileCoord tc = tile_coord(p, w, BN);
             if (tc.skip) continue;
-            const uint32_t buf = lt & 1u;
+            const uint32_t buf = lt % S::NACC;
             float* cbase = to_partial ? p.partial + (int64_t)tc.split * p.M * p.N : p.C + (int64_t)tc.b_out * p.c_so + (int64_t)tc.b_in * p.c_si;
             const int64_t ld = to_partial ? p.N : p.ldc;
             const float alpha = to_partial ? 1.0f : p.alpha, beta = to_partial ? 0.0f : p.beta;
@@ -698,7 +701,7 @@ __global__ void __launch_bounds__(TcSmem<BN, A_TM>::THREADS, (BN == 64 ? 2 : 1))
                     if (r < p.M) asm volatile("prefetch.global.L2 [%0];" ::"l"(sm_probs + (cbase - p.C) + r * ld + col0 + 32 * (i % lines)));
                 }
             }
-            ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt >> 1) & 1u, p.status, 4)) != 0);
+            ok = TR_WAIT(__all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt / S::NACC) & 1u, p.status, 4)) != 0);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
