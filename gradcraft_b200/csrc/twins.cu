@@ -44,15 +44,22 @@ __global__ void __launch_bounds__(256) presplit_kernel(const TwinJob* __restrict
         const TwinJob j = jobs[lo];
         const int64_t i = g - j.first;
         const int64_t n_groups = (j.N + 7) / 8, k_chunks = ((j.K + 15) / 16) * 2;
-        // thread order: n fastest for the K x N storage (coalesced along n), k chunk fastest for the N x K storage (coalesced along k)
+        // thread order: n fastest for the K x N storage (reads coalesced along n); for the N x K storage the eight rows of a
+        // core matrix are neighbours (n % 8 fastest, then the k chunk), so that eight threads write one whole 128-byte line of
+        // the output and each reads the 32 bytes of its row with two vector loads
         int64_t n, kc;
         if (j.kn) { n = i % (n_groups * 8); kc = i / (n_groups * 8); }
-        else { kc = i % k_chunks; n = i / k_chunks; }
+        else { const int64_t q = i >> 3; kc = q % k_chunks; n = (q / k_chunks) * 8 + (i & 7); }
         float x[8];
+        if (!j.kn && n < j.N && kc * 8 + 8 <= j.K && ((reinterpret_cast<uintptr_t>(j.W) | (uintptr_t)(j.ld * 4)) & 15) == 0) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(j.W + n * j.ld + kc * 8)), b = __ldg(reinterpret_cast<const float4*>(j.W + n * j.ld + kc * 8 + 4));
+            x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const int64_t k = kc * 8 + e;
-            x[e] = (n < j.N && k < j.K) ? (j.kn ? j.W[k * j.ld + n] : j.W[n * j.ld + k]) : 0.0f;
+            for (int e = 0; e < 8; ++e) {
+                const int64_t k = kc * 8 + e;
+                x[e] = (n < j.N && k < j.K) ? (j.kn ? j.W[k * j.ld + n] : j.W[n * j.ld + k]) : 0.0f;
+            }
         }
         float s[8];
 #pragma unroll
