@@ -19,6 +19,14 @@ static int dispatch_gemm(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g, cons
         if (rc == GCB_OK && g.gelu_act) rc = gcb_gelu_fwd_f32(ctx, g.gelu_act, g.C, g.M * g.N);
         return rc;
     }
+    if (rc == GCB_UNSUPPORTED && g.residual) {
+        // no kernel with the residual epilogue takes this problem: the same product, then the addition as a pass of its own (same order of operations)
+        GemmArgs plain = g;
+        plain.residual = nullptr;
+        rc = dispatch_gemm(ctx, ta, tb, plain, who);
+        if (rc == GCB_OK) rc = gcb_binary_f32(ctx, GCB_B_ADD, g.C, g.C, g.residual, g.M * g.N);
+        return rc;
+    }
     if (rc == GCB_UNSUPPORTED && g.colsum) {
         // no kernel gathers the column sums of op(B) for this problem: the same product, then the row reduction as a pass of its own
         GemmArgs plain = g;
@@ -136,6 +144,15 @@ int gcb_linear_gelu_fwd_f32(gcb_ctx* ctx, int op_b, int64_t M, int64_t N, int64_
     GemmArgs g{M, N, K, 1.0f, 0.0f, x, W, bias, pre, lda, ldb, N, 0, 0, 0, 0, 0, 0, 1, 1};
     g.gelu_act = act;
     return run_gemm(ctx, GCB_OP_N, op_b, g, "gcb_linear_gelu_fwd_f32");
+}
+
+int gcb_linear_residual_f32(gcb_ctx* ctx, int op_b, int64_t M, int64_t N, int64_t K, const float* x, int64_t lda, const float* W, int64_t ldb, const float* bias, const float* residual, float* out) {
+    GCB_REQUIRE(ctx, "gcb_linear_residual_f32: ctx is NULL");
+    GCB_REQUIRE(M == 0 || N == 0 || (residual && out), "gcb_linear_residual_f32: NULL residual / out");
+    GCB_REQUIRE(residual != out, "gcb_linear_residual_f32: out must not alias residual");
+    GemmArgs g{M, N, K, 1.0f, 0.0f, x, W, bias, out, lda, ldb, N, 0, 0, 0, 0, 0, 0, 1, 1};
+    g.residual = residual;
+    return run_gemm(ctx, GCB_OP_N, op_b, g, "gcb_linear_residual_f32");
 }
 
 int gcb_profile_gemm_begin(gcb_ctx* ctx) {

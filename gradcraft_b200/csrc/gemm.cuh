@@ -19,6 +19,9 @@ struct GemmArgs {
     const float* gelu_pre = nullptr;
     // GELU-forward epilogue: besides C, gelu(C[m,n]) is written to gelu_act, laid out like C
     float* gelu_act = nullptr;
+    // residual epilogue (needs beta == 0, no GELU epilogue, unbatched): C[m,n] = alpha * (op(A) op(B))[m,n] + bias[n] + residual[m,n]; residual is laid out
+    // like C and must not alias it
+    const float* residual = nullptr;
     const float* sm_probs = nullptr;
     const float* sm_rowdot = nullptr;
     float sm_scale = 1.0f;

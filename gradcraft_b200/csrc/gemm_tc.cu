@@ -62,6 +62,7 @@ struct TcParams {
     int colsum_accumulate;
     const float* gelu_pre;   // GELU-backward epilogue (see GemmArgs), or NULL: applied by the pair kernel only
     float* gelu_act;         // GELU-forward second output (see GemmArgs), or NULL: pair kernel only
+    const float* resid;      // residual added in the epilogue (see GemmArgs), or NULL: pair kernel only
     const float* sm_probs;   // softmax-backward epilogue (see GemmArgs), or NULL
     const float* sm_rowdot;
     float sm_scale;
@@ -1076,7 +1077,7 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
         const bool to_partial = p.splits > 1;
         // the float4 fast path needs C and the GELU side arrays (laid out like C) on 16-byte boundaries; otherwise the scalar path runs
         const bool vec_ok = to_partial ? (p.N % 4 == 0)
-                                       : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.gelu_pre) | reinterpret_cast<uintptr_t>(p.gelu_act) |
+                                       : (p.ldc % 4 == 0 && ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.gelu_pre) | reinterpret_cast<uintptr_t>(p.gelu_act) | reinterpret_cast<uintptr_t>(p.resid) |
                                                               (uintptr_t)(p.c_so * 4) | (uintptr_t)(p.c_si * 4)) & 15) == 0);
         const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
         const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;
@@ -1092,13 +1093,15 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
             const float* bias = to_partial ? nullptr : p.bias;
             const float* gelu_pre = to_partial ? nullptr : p.gelu_pre;
             float* gelu_act = to_partial ? nullptr : p.gelu_act;
+            const float* resid = to_partial ? nullptr : p.resid;
+            const float* side = gelu_pre ? gelu_pre : resid;  // a second input laid out like C (the launcher never sets both)
             const int64_t mrow0 = (int64_t)tc.m0 + 128 * (int)rank + 32 * q;
-            if (gelu_pre) {  // pull this warp's part of the pre-activation tile into L2 while the tile's MMAs are still running
+            if (side) {  // pull this warp's part of the side input's tile into L2 while the tile's MMAs are still running
                 const int64_t col0 = (int64_t)tc.n0 + 32 * c_begin;
                 const int lines = (int)max((int64_t)0, (min(p.N, (int64_t)tc.n0 + 32 * c_end) - col0 + 31) / 32);
                 for (int i = lane; i < 32 * lines; i += 32) {
                     const int64_t r = mrow0 + i / lines;
-                    if (r < p.M) asm volatile("prefetch.global.L2 [%0];" ::"l"(gelu_pre + (cbase - p.C) + r * ld + col0 + 32 * (i % lines)));
+                    if (r < p.M) asm volatile("prefetch.global.L2 [%0];" ::"l"(side + (cbase - p.C) + r * ld + col0 + 32 * (i % lines)));
                 }
             }
             ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (lt / NACC) & 1u, p.status, 14)) != 0;
@@ -1112,9 +1115,9 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                 if (p.dbg & 4) break;
 #endif
                 const bool blk_fast = vec_ok && mrow0 + 32 <= p.M && nb + 32 <= p.N;  // whole 32 x 32 block in bounds
-                float4 gp[8];  // GELU-backward epilogue: the block's pre-activations are requested before the accumulator is read
-                if (gelu_pre && blk_fast) {
-                    const float* pp = gelu_pre + (cbase - p.C) + (mrow0 + sub_r) * ld + nb + sub_c;
+                float4 gp[8];  // GELU-backward / residual epilogue: the block's side input is requested before the accumulator is read
+                if (side && blk_fast) {
+                    const float* pp = side + (cbase - p.C) + (mrow0 + sub_r) * ld + nb + sub_c;
 #pragma unroll
                     for (int r4 = 0; r4 < 8; ++r4) gp[r4] = ld4(pp + (int64_t)r4 * 4 * ld);
                 }
@@ -1137,6 +1140,7 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                             o.x = fmaf(o.x, alpha, bb.x); o.y = fmaf(o.y, alpha, bb.y); o.z = fmaf(o.z, alpha, bb.z); o.w = fmaf(o.w, alpha, bb.w);
                             if (beta != 0.0f) { const float4 old = ld4(dst); o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y); o.z = fmaf(beta, old.z, o.z); o.w = fmaf(beta, old.w, o.w); }
                             if (gelu_pre) { o.x *= gelu_grad_f(gp[r4].x); o.y *= gelu_grad_f(gp[r4].y); o.z *= gelu_grad_f(gp[r4].z); o.w *= gelu_grad_f(gp[r4].w); }
+                            if (resid) { o.x += gp[r4].x; o.y += gp[r4].y; o.z += gp[r4].z; o.w += gp[r4].w; }
                             st4(dst, o);
                             if (gelu_act) st4(gelu_act + (dst - p.C), make_float4(gelu_f(o.x), gelu_f(o.y), gelu_f(o.z), gelu_f(o.w)));
                         }
@@ -1152,6 +1156,7 @@ __global__ void __launch_bounds__(PairSmemT<A_TM>::THREADS, 1) gemm_tc_pair_kern
                                     if (bias) r += bias[n + u];
                                     if (beta != 0.0f) r += beta * d[u];
                                     if (gelu_pre) r *= gelu_grad_f(gelu_pre[(d - p.C) + u]);
+                                    if (resid) r += resid[(d - p.C) + u];
                                     d[u] = r;
                                     if (gelu_act) gelu_act[(d - p.C) + u] = gelu_f(r);
                                 }
@@ -1383,8 +1388,8 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     p.dbg = getenv("GRADC_TC_DBG") ? atoi(getenv("GRADC_TC_DBG")) : 0;
 #endif
     p.sm_probs = g.sm_probs; p.sm_rowdot = g.sm_rowdot; p.sm_scale = g.sm_scale;
-    p.gelu_pre = g.gelu_pre; p.gelu_act = g.gelu_act;
-    if ((g.gelu_pre || g.gelu_act) && !use_pair) return GCB_UNSUPPORTED;  // only the pair kernel carries this epilogue; the caller applies it as a second pass instead
+    p.gelu_pre = g.gelu_pre; p.gelu_act = g.gelu_act; p.resid = g.residual;
+    if ((g.gelu_pre || g.gelu_act || g.residual) && !use_pair) return GCB_UNSUPPORTED;  // only the pair kernel carries these epilogues; the caller applies them as a second pass instead
     static const int pair_tmem_env = [] { const char* e = getenv("GRADC_TC_PAIR_ATMEM"); return e ? atoi(e) : 1; }();
     const bool pair_a_tmem = pair_tmem_env != 0 && ctx->gemm_split_mode == 2;
     // column sums of op(B): gathered by the B-splitter warps of the pair kernel (A through tensor memory) from B stored K x N
@@ -1395,7 +1400,7 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     // split-K when the tiles alone would leave SMs idle: pick the slice count with the lowest modelled time
     // (rounds of 148 persistent CTAs x K blocks per slice, plus writing and re-reading the partial tiles)
     int splits = 1;
-    if (batches == 1 && p.k_blocks_total >= 64 && g.causal == 0 && !g.gelu_pre && !g.gelu_act) {
+    if (batches == 1 && p.k_blocks_total >= 64 && g.causal == 0 && !g.gelu_pre && !g.gelu_act && !g.residual) {
         const int ctas = use_pair ? kSMs / 2 : kSMs * (BN == 64 ? 2 : 1);
         double best = 1e30;
         for (int sp = 1; sp <= 32 && p.k_blocks_total / sp >= 16; ++sp) {
@@ -1466,7 +1471,7 @@ int gemm_tc_launch(gcb_ctx* ctx, bool ta, bool tb, const GemmArgs& g) {
     else if (BN == 128) rc = a_tmem ? launch_bn<128, true>(ctx, ta, tb, ma, mb, mc, mp, p, grid) : launch_bn<128, false>(ctx, ta, tb, ma, mb, mc, mp, p, grid);
     else rc = a_tmem ? launch_bn<64, true>(ctx, ta, tb, ma, mb, mc, mp, p, grid) : launch_bn<64, false>(ctx, ta, tb, ma, mb, mc, mp, p, grid);
     if (rc) return rc;
-    const char* family = use_pair ? (g.gelu_act ? "gemm_tc_pair_gelu_fwd" : g.gelu_pre ? "gemm_tc_pair_gelu_bwd" : "gemm_tc_pair")
+    const char* family = use_pair ? (g.gelu_act ? "gemm_tc_pair_gelu_fwd" : g.gelu_pre ? "gemm_tc_pair_gelu_bwd" : g.residual ? "gemm_tc_pair_residual" : "gemm_tc_pair")
                          : BN == 256 ? (g.sm_probs ? "gemm_tc_256_softmax_bwd" : "gemm_tc_256") : BN == 128 ? "gemm_tc_128" : "gemm_tc_64";
     rc = after_launch(ctx, family);
     if (rc) return rc;

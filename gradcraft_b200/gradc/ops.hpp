@@ -296,16 +296,7 @@ class AddNode : public Node<float> {
 
 public:
     AddNode(Tensor<float> l, Tensor<float> r, int64_t outer, int64_t inner) : m_left(std::move(l)), m_right(std::move(r)), m_outer(outer), m_inner(inner) {}
-    Tensor<float> realize() override {
-        m_left.realize();
-        m_right.realize();
-        Tensor<float> a = make_contiguous(m_left), b = make_contiguous(m_right);
-        Tensor<float> out(m_left.shape(), m_left.device(), uninitialized);
-        gcb_ctx* c = ctx_of(out);
-        if (m_outer == 1) gcb_check(gcb_binary_f32(c, GCB_B_ADD, out.data_ptr(), a.data_ptr(), b.data_ptr(), m_inner), "add");
-        else gcb_check(gcb_binary_rowvec_f32(c, GCB_B_ADD, out.data_ptr(), a.data_ptr(), b.data_ptr(), m_outer, m_inner), "broadcast add");
-        return out;
-    }
+    Tensor<float> realize() override;  // defined after MatMulNode: x + linear(...) becomes one GEMM with the addition in its epilogue
     void backward(const Tensor<float>& g, bool) override {
         push_grad(m_left, g);  // the residual branch adopts the gradient buffer: no copy
         if (!m_right.requires_grad()) return;
@@ -529,8 +520,10 @@ public:
     MatMulNode(Tensor<float> x, Tensor<float> w, Tensor<float> b, int64_t M, int64_t K, int64_t N, std::vector<int64_t> out_shape)
         : m_x(std::move(x)), m_w(std::move(w)), m_b(std::move(b)), m_M(M), m_K(K), m_N(N), m_out_shape(std::move(out_shape)) {}
     Tensor<float> realize() override { return realize_impl(nullptr); }
-    // y = x W + b, and gelu(y) into *gelu_out (allocated here) when that is asked for: one GEMM with two outputs
-    Tensor<float> realize_impl(Tensor<float>* gelu_out) {
+    // y = x W + b, and gelu(y) into *gelu_out (allocated here) when that is asked for: one GEMM with two outputs.
+    // With `residual` (dense, of the output's size) the result is (x W + b) + residual instead: the residual add of a
+    // transformer block rides in the GEMM's epilogue and y itself is never written.
+    Tensor<float> realize_impl(Tensor<float>* gelu_out, const Tensor<float>* residual = nullptr) {
         m_x.realize();
         m_w.realize();
         const bool has_bias = m_b._get_state() != nullptr;
@@ -544,10 +537,16 @@ public:
                                               gelu_out->data_ptr()), "linear + gelu");
             return out;
         }
+        if (residual != nullptr) {
+            gcb_check(gcb_linear_residual_f32(ctx_of(out), w.transposed ? GCB_OP_T : GCB_OP_N, m_M, m_N, m_K, m_x.data_ptr(), m_K, w.p, w.ld, has_bias ? m_b.data_ptr() : nullptr,
+                                              residual->data_ptr(), out.data_ptr()), "linear + residual");
+            return out;
+        }
         gcb_check(gcb_gemm_f32(ctx_of(out), GCB_OP_N, w.transposed ? GCB_OP_T : GCB_OP_N, m_M, m_N, m_K, 1.0f, m_x.data_ptr(), m_K, w.p, w.ld, 0.0f, out.data_ptr(), m_N,
                                has_bias ? m_b.data_ptr() : nullptr), "matmul");
         return out;
     }
+    int64_t out_volume() const { return m_M * m_N; }
     void backward(const Tensor<float>& g, bool) override {
         Tensor<float> gc = make_contiguous(g);
         gcb_ctx* c = ctx_of(gc);
@@ -605,6 +604,26 @@ public:
         return v;
     }
 };
+
+inline Tensor<float> AddNode::realize() {
+    m_left.realize();
+    // x + linear(...), the linear layer's output held by nobody but this node and not yet computed: the GEMM adds x in its
+    // epilogue ((x W + b) + x, the order the two nodes would have used) and the linear layer's own output is never written.
+    // Its backward needs only the gradient, which AddNode::backward hands on as before.
+    if (m_outer == 1 && m_left.is_contiguous()) {
+        auto st = m_right._get_state();
+        auto* mm = dynamic_cast<MatMulNode*>(st->m_creation_op.get());
+        if (mm != nullptr && !st->m_is_realized && st.use_count() == 2 /* m_right and st */ && mm->out_volume() == m_inner && m_right.is_contiguous() && m_right.offset() == 0)
+            return mm->realize_impl(nullptr, &m_left);
+    }
+    m_right.realize();
+    Tensor<float> a = make_contiguous(m_left), b = make_contiguous(m_right);
+    Tensor<float> out(m_left.shape(), m_left.device(), uninitialized);
+    gcb_ctx* c = ctx_of(out);
+    if (m_outer == 1) gcb_check(gcb_binary_f32(c, GCB_B_ADD, out.data_ptr(), a.data_ptr(), b.data_ptr(), m_inner), "add");
+    else gcb_check(gcb_binary_rowvec_f32(c, GCB_B_ADD, out.data_ptr(), a.data_ptr(), b.data_ptr(), m_outer, m_inner), "broadcast add");
+    return out;
+}
 
 inline Tensor<float> GeLUNode::realize() {
     auto st = m_parent._get_state();

@@ -191,6 +191,12 @@ GCB_API int gcb_gemm_batched_softmax_bwd_f32(gcb_ctx* ctx, int op_a, int op_b, i
 GCB_API int gcb_linear_gelu_fwd_f32(gcb_ctx* ctx, int op_b, int64_t M, int64_t N, int64_t K, const float* x, int64_t lda, const float* W, int64_t ldb, const float* bias,
                             float* pre, float* act);
 
+/* out = (x op(W) + bias) + residual, all M x N and dense (leading dimension N), out must not alias residual: Linear::forward
+ * (nn/layers/linear.hpp:22-25) followed by the residual AddNode of a transformer block (graph/nodes/math_nodes.hpp:47-90;
+ * nn/layers/gpt.hpp:62-63), in that order of additions, without materialising the linear layer's own output. */
+GCB_API int gcb_linear_residual_f32(gcb_ctx* ctx, int op_b, int64_t M, int64_t N, int64_t K, const float* x, int64_t lda, const float* W, int64_t ldb, const float* bias,
+                            const float* residual, float* out);
+
 /* dpre = (op(A) op(B)) * gelu'(pre), M x N, pre and dpre dense (leading dimension N): the backward of y = gelu(pre) folded
  * into the GEMM that produces dy (dX of the linear layer that consumed y; reference: NormalMatMulNode::backward
  * math_nodes.hpp:475-535 followed by GeLUNode::backward activation_nodes.hpp:157-192 and its BGeLU kernel). */

@@ -257,6 +257,38 @@ def test_linear_gelu_forward_two_outputs(env, M, N, K):
     assert torch.equal(again, act)
 
 
+@pytest.mark.parametrize("M,N,K,opb,with_bias", [(512, 512, 256, 0, True), (768, 256, 1024, 1, False), (96, 80, 48, 0, True), (300, 260, 64, 1, True)])
+def test_linear_with_residual_epilogue(env, M, N, K, opb, with_bias):
+    """out = (x op(W) + b) + r from one call: the CTA-pair kernel's residual epilogue (whole and ragged tiles) and the two-pass
+    fallback for shapes it does not take, against float64; where the plain GEMM runs unsliced the result equals GEMM + add bit
+    for bit (same order of additions)."""
+    ctx, torch, capi = env
+    x, W, bias, r = rnd(80, M, K), (rnd(81, N, K) if opb else rnd(81, K, N)) * 0.1, rnd(82, N), rnd(83, M, N) * 3
+    X, Wd, Bd, R = (torch.from_numpy(a).cuda() for a in (x, W, bias, r))
+    out = torch.full((M, N), float("nan"), device="cuda")
+    ctx.ctx_set_gemm_engine(0)
+    try:
+        before = ctx.ctx_launch_count_named(b"gemm_tc_pair_residual")
+        ctx.linear_residual_f32(opb, M, N, K, X, K, Wd, W.shape[1], Bd if with_bias else None, R, out)
+        plain = torch.empty_like(out)
+        ctx.gemm_f32(0, opb, M, N, K, 1.0, X, K, Wd, W.shape[1], 0.0, plain, N, Bd if with_bias else None)
+        ctx.binary_f32(0, plain, plain, R, M * N)  # GCB_B_ADD
+        ctx.sync()
+        fused = ctx.ctx_launch_count_named(b"gemm_tc_pair_residual") - before
+    finally:
+        ctx.ctx_set_gemm_engine(2)
+    ref = x.astype(np.float64) @ (W.T if opb else W).astype(np.float64) + (bias if with_bias else 0.0) + r
+    assert max_abs_rel(out.cpu().numpy(), ref) < 1e-5
+    if K < 1024:  # longer K loops on few tiles make the plain GEMM cut K into slices, which the residual form does not: another summation order
+        assert torch.equal(out, plain)
+    else:
+        assert max_abs_rel(out.cpu().numpy(), plain.cpu().numpy()) < 1e-5
+    assert fused == (1 if M > 128 and N > 128 and K >= 256 else 0)  # small or short-K shapes go through the fallback
+    with pytest.raises(capi.GcbError) as e:
+        ctx.linear_residual_f32(opb, M, N, K, X, K, Wd, W.shape[1], None, out, out)  # out aliases the residual
+    assert e.value.status == capi.INVALID_ARG
+
+
 def test_pair_kernel_batched_and_causal_paths(env):
     """Head dimension 256 sends every attention GEMM to the CTA-pair kernel (N = 256 or K >= 256): batched operands with
     two-level strides and all three causal variants there, against float64."""

@@ -74,14 +74,14 @@ def test_mid_size_training_step_runs_the_full_size_kernels_and_matches_reference
     epilogues), split-K weight gradients, the 256-wide dS GEMM with the softmax backward in its epilogue, the 64-wide causal
     attention GEMMs and the staged LayerNorm backward, i.e. the kernels the full-size benchmark runs, and is held to the
     same loss / gradient / weight bar against the compiled reference (3 steps with clipping)."""
-    run_case("mid_lngelu", families=("gemm_tc_pair", "gemm_tc_pair_gelu_fwd", "gemm_tc_pair_gelu_bwd", "splitk_reduce", "gemm_tc_256_softmax_bwd", "gemm_tc_64",
+    run_case("mid_lngelu", families=("gemm_tc_pair", "gemm_tc_pair_gelu_fwd", "gemm_tc_pair_gelu_bwd", "gemm_tc_pair_residual", "splitk_reduce", "gemm_tc_256_softmax_bwd", "gemm_tc_64",
                                      "layernorm_bwd_ring", "adamw_arena", "scatter_accumulate", "scatter_fold", "softmax_ce_bwd"))
 
 
 def test_mid_size_rmsnorm_swiglu_training_step_matches_reference():
     """The reference's own GPT (RMSNorm + SwiGLU) at 5120 rows: the staged RMSNorm backward, the fused SwiGLU kernels and the
     CTA-pair GEMM on 768-wide outputs, held to the loss / gradient / weight bar against the compiled reference (3 steps, clip)."""
-    run_case("mid_rmsswiglu", families=("gemm_tc_pair", "splitk_reduce", "gemm_tc_256_softmax_bwd", "gemm_tc_64", "rmsnorm_bwd_ring", "swiglu_fwd", "swiglu_bwd", "adamw_arena",
+    run_case("mid_rmsswiglu", families=("gemm_tc_pair", "gemm_tc_pair_residual", "splitk_reduce", "gemm_tc_256_softmax_bwd", "gemm_tc_64", "rmsnorm_bwd_ring", "swiglu_fwd", "swiglu_bwd", "adamw_arena",
                                         "scatter_accumulate", "scatter_fold", "softmax_ce_bwd"))
 
 
