@@ -435,7 +435,7 @@ def test_bad_targets_are_reported_not_dereferenced(env):
     ctx.sync()  # the flag is cleared; the context stays usable
 
 
-@pytest.mark.parametrize("n,V,W", [(64, 23, 12), (4096, 512, 128), (32768, 4096, 1024), (3000, 100, 36), (100, 10, 7), (5000, 50, 2052)])
+@pytest.mark.parametrize("n,V,W", [(64, 23, 12), (4096, 512, 128), (32768, 4096, 1024), (3000, 100, 36), (100, 10, 7), (5000, 50, 2052), (50000, 100003, 8), (33, 5, 4)])
 def test_scatter_add_vs_oracle_and_determinism(env, n, V, W):
     ctx, torch, capi = env
     idx = synth.zipf_tokens(60, n, V)  # Zipf(1.1): heavy head rows
