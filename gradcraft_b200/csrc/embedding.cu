@@ -395,7 +395,8 @@ static int build_plan(gcb_ctx* ctx, Scratch& sc, ScatterPlan& p, const IdxT* idx
     p.order = (int32_t*)base; base += b_ord;
     p.parked = b_park ? (float*)base : nullptr;
     GCB_CHECK_CUDA(cudaMemsetAsync(p.blk, 0, b_blk, ctx->stream));
-    GCB_CHECK_CUDA(launch_chained(ctx->stream, (unsigned)std::min<int64_t>((n + 255) / 256, (int64_t)kSMs * 8), 256, 0, scatter_hist_kernel<IdxT>, p.blk, idx, n, vocab, ctx->d_status));
+    // the first kernel follows a memset, not a kernel: launched the ordinary way (its pdl_wait is then a no-op)
+    scatter_hist_kernel<IdxT><<<(unsigned)std::min<int64_t>((n + 255) / 256, (int64_t)kSMs * 8), 256, 0, ctx->stream>>>(p.blk, idx, n, vocab, ctx->d_status);
     rc = after_launch(ctx, "scatter_hist"); if (rc) return rc;
     GCB_CHECK_CUDA(launch_chained(ctx->stream, (unsigned)n_blocks, 256, 0, scatter_colsum_kernel, p.blk, p.counts, p.blocktot, p.n_chunks, vocab));
     rc = after_launch(ctx, "scatter_colsum"); if (rc) return rc;
